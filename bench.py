@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the mapreduce / scan / sort hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--detail 0|1]
+
+Headline workload (one "step"): the single-GPU scan configuration the metric is quoted on —
+inclusive `scan!(+)` over Float32 n=2^28 (x ~ U[0,1)) and over UInt32 n=2^28 (x ~ U{0..255}),
+i.e. 2 * 8n = 4.29 GB of algorithmic traffic per GPU per step. With N > 1 every rank holds its own
+2^28-element shard of one global array of N*2^28 elements (weak scaling); a step is the sharded
+scan: local reduce, NCCL allgather of the shard totals, local scan seeded with the carry.
+
+`value` is whole-job effective GB/s (algorithmic bytes / device time) with the inputs resident in
+HBM; `e2e` is the same metric through the host-buffer API (pinned host arrays in, host arrays out,
+copies inside the timed region). `roofline` describes the dominant kernel (the look-back scan
+kernel) against the measured HBM copy peak; `cpu_baseline` is the Base-like CPU code of oracle/
+timed on this host; `primitives` lists the other configurations (mapreduce, affine scan, sorts)
+measured the same way after the timed region.
+
+`--impl reference` times the reference's CPU path (Julia Base semantics restated in oracle/,
+the reference itself being Julia, which this machine does not have) with all host threads, on a
+bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_HEADLINE = 1 << 28
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for p in self.samples:
+            try:
+                sm.append(float(p[0]))
+                mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm (oracle/: the Base-like restatement)
+# ---------------------------------------------------------------------------------------------
+def cpu_scan_sample(threads, n, repeats=3):
+    """Times accumulate(+) over Float32 and UInt32 arrays of n elements; returns (GB/s, seconds per pass)."""
+    import numpy as np
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    xf = rng.random(n, dtype=np.float32)
+    xu = rng.integers(0, 256, n).astype(np.uint32)
+    of, ou = np.empty_like(xf), np.empty_like(xu)
+    O.base_accumulate(xf, of, threads)  # warm the pages
+    O.base_accumulate(xu, ou, threads)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O.base_accumulate(xf, of, threads)
+        O.base_accumulate(xu, ou, threads)
+        best = min(best, time.perf_counter() - t0)
+    return 2 * 8 * n / best / 1e9, best
+
+
+def cpu_baseline_object(threads, n):
+    gbs, secs = cpu_scan_sample(threads, n)
+    gbs1, _ = cpu_scan_sample(1, n, repeats=2) if threads > 1 else (gbs, secs)
+    return {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "value_1_thread": round(gbs1, 3),
+            "sample": "accumulate(+) over Float32 and UInt32 arrays of n=2^%d (1/%d of the 2^28 workload), "
+                      "best of 3, C restatement of Base.accumulate (oracle/kf_oracle.c)" % (
+                          n.bit_length() - 1, N_HEADLINE // n)}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import oracle as O
+    threads = O.max_threads()
+    n = 1 << 26
+    for _ in range(args.warmup):
+        cpu_scan_sample(threads, n, repeats=1)
+    t0 = time.perf_counter()
+    vals = [cpu_scan_sample(threads, n, repeats=1) for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    secs = sum(v[1] for v in vals)
+    gbs = args.steps * 2 * 8 * n / secs / 1e9
+    line = {
+        "impl": "reference", "metric": "effective GB/s, inclusive scan(+), Float32 + UInt32", "value": round(gbs, 3),
+        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(1e3 * secs / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32+u32", "data": "synthetic",
+        "config": {"workload": "inclusive scan!(+): Float32 U[0,1) and UInt32 U{0..255}; CPU sample n=2^26 per array "
+                               "per step (1/4 of the 2^28 GPU workload)", "threads": threads},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "n=2^26 per array per step; KernelForge.jl is Julia (not installed here), so the "
+                                   "CPU path is the C restatement of Base.accumulate in oracle/kf_oracle.c"},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": round(wall, 2),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def time_gpu(fn, iters, torch, sync_each=False):
+    """Average milliseconds per call of fn(), CUDA events on the current stream."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(iters):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / iters
+
+
+def primitives_table(kf, torch, peak, iters=10):
+    """Effective GB/s of every other configuration of the path at its full size, one GPU."""
+    out = {}
+    n = N_HEADLINE
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def add(name, nbytes, ms, launches):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4),
+                     "frac_of_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 4), "algorithmic_bytes": nbytes,
+                     "kernel_launches": launches}
+
+    xf = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+    dst1 = torch.empty(1, dtype=torch.float32, device="cuda")
+    tmp = kf.get_allocation(kf.MapReduce1D, kf.identity, "+", xf)
+    fn = lambda: kf.mapreduce_(kf.identity, "+", dst1, xf, tmp=tmp)
+    for _ in range(3):
+        fn()
+    add("mapreduce_f32_sum_2p28", 4 * n, time_gpu(fn, iters * 2, torch), 1)
+    fn = lambda: kf.mapreduce_(kf.abs2, "+", dst1, xf[: 1 << 20], tmp=tmp)
+    for _ in range(3):
+        fn()
+    add("mapreduce_f32_abs2_2p20", 4 << 20, time_gpu(fn, 200, torch), 1)
+
+    na = 1 << 26
+    a = 0.5 + 0.5 * torch.rand(na, dtype=torch.float32, device="cuda", generator=g)
+    b = 2.0 * torch.rand(na, dtype=torch.float32, device="cuda", generator=g) - 1.0
+    da, db = torch.empty_like(a), torch.empty_like(b)
+    tmpa = kf.get_allocation(kf.Scan1D, kf.identity, kf.AffineCompose(), (a, b))
+    fn = lambda: kf.scan_(kf.AffineCompose(), (da, db), (a, b), tmp=tmpa)
+    for _ in range(3):
+        fn()
+    add("scan_affine_f32x2_2p26", 16 * na, time_gpu(fn, iters * 2, torch), 1)
+    del a, b, da, db, tmpa
+
+    def rand_u32():
+        return torch.randint(0, 1 << 32, (n,), dtype=torch.int64, device="cuda", generator=g).to(torch.int32).view(torch.uint32)
+
+    keys = rand_u32()
+    work = torch.empty_like(keys)
+    tmps = kf.get_allocation(kf.Sort1D, keys)
+
+    def sort_once(src, ws):
+        # out of place: the unsorted input is read again every iteration, nothing to restore
+        kf.sort_(work.view(src.dtype), src, tmp=ws)
+
+    for _ in range(2):
+        sort_once(keys, tmps)
+    add("sort_u32_keys_2p28", 36 * n, time_gpu(lambda: sort_once(keys, tmps), iters, torch), 6)
+    kfl = torch.randn(n, dtype=torch.float32, device="cuda", generator=g)
+    for _ in range(2):
+        sort_once(kfl, tmps)
+    add("sort_f32_keys_2p28", 36 * n, time_gpu(lambda: sort_once(kfl, tmps), iters, torch), 6)
+    del kfl, tmps
+    idx = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
+    vout = torch.empty_like(idx)
+    tmpp = kf.get_allocation(kf.Sort1D, idx, keys=keys)
+    fnp = lambda: kf.sort_(vout, idx, keys=keys, keys_dst=work, tmp=tmpp)
+    for _ in range(2):
+        fnp()
+    add("sort_u32_keys_u32_payload_2p28", 68 * n, time_gpu(fnp, iters, torch), 6)
+    return out
+
+
+def run_gpu_arm(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    kf = load_package()
+    from kernelforge_jl_b200 import distributed as kfd
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peak, peak_kind = measured_peak()
+    n = N_HEADLINE
+
+    # Each rank owns shard `rank` of a global array of world*n elements (seeded per shard).
+    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    xf = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+    xu = torch.randint(0, 256, (n,), dtype=torch.int32, device="cuda", generator=g).view(torch.uint32)
+    df, du = torch.empty_like(xf), torch.empty_like(xu)
+    tmp_f = kf.get_allocation(kf.Scan1D, kf.identity, "+", xf)
+    tmp_u = kf.get_allocation(kf.Scan1D, kf.identity, "+", xu)
+    group = kfd.ShardGroup() if world > 1 else None
+
+    def step():
+        if world == 1:
+            kf.scan_("+", df, xf, tmp=tmp_f)
+            kf.scan_("+", du, xu, tmp=tmp_u)
+        else:
+            kfd.scan_(group, "+", df, xf, tmp=tmp_f)
+            kfd.scan_(group, "+", du, xu, tmp=tmp_u)
+
+    launches_per_step = 2 if world == 1 else 6  # sharded: reduce + scan of the shard totals + seeded scan, per array
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    barrier()
+    ms = start.elapsed_time(stop)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    step_bytes = world * 2 * 8 * n
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # quick device-side sanity of the timed outputs (wrapping differences reproduce the input)
+    ok = bool(((du.view(torch.int32)[1:] - du.view(torch.int32)[:-1]) == xu.view(torch.int32)[1:]).all().item())
+    if not ok:
+        raise SystemExit("bench: scan output failed its difference check")
+
+    # ---- roofline of the dominant kernel: the UInt32/Float32 look-back scan kernel, single GPU view
+    kern_ms = time_gpu(lambda: kf.scan_("+", du, xu, tmp=tmp_u), 20, torch)
+    achieved = 8 * n / (kern_ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(tpath) as fh:
+            traffic = json.load(fh).get("scan_kernel_u32_2p28_bytes_per_launch")
+    except Exception:
+        pass
+    roofline = {"bound": "hbm", "kernel": "scan_kernel<uint32, +, 512x4>", "achieved": round(achieved, 1),
+                "peak": peak, "peak_kind": peak_kind + " (STREAM-style copy)", "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
+                "algorithmic_bytes_per_launch": 8 * n, "kernel_ms": round(kern_ms, 4), "traffic": traffic}
+
+    # ---- end to end through the host-buffer API: pinned host arrays in, host arrays out
+    e2e = None
+    if True:
+        hf = torch.empty(n, dtype=torch.float32).pin_memory()
+        hu = torch.empty(n, dtype=torch.int32).pin_memory()
+        hf.copy_(xf)
+        hu.copy_(xu.view(torch.int32))
+        of = torch.empty(n, dtype=torch.float32).pin_memory()
+        ou = torch.empty(n, dtype=torch.int32).pin_memory()
+        pipe = kfd.HostScanPipeline(kf, n, chunks=8)
+
+        def e2e_step():
+            pipe.scan_host("+", of, hf)
+            pipe.scan_host("+", ou.view(torch.uint32) if hasattr(torch, "uint32") else ou, hu.view(torch.uint32))
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e_start.record()
+        e_steps = max(2, min(args.steps, 5))
+        for _ in range(e_steps):
+            e2e_step()
+        e_stop.record()
+        barrier()
+        e_ms = e_start.elapsed_time(e_stop) / e_steps
+        if world > 1:
+            t = torch.tensor([e_ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        okh = bool((ou[1:] - ou[:-1] == hu[1:]).all().item())
+        if not okh:
+            raise SystemExit("bench: host-pipeline scan output failed its difference check")
+        e2e = {"value": round(world * 2 * 8 * n / (e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": 2 * 4 * n, "d2h_bytes_per_step": 2 * 4 * n, "ms_per_step": round(e_ms, 3),
+               "note": "independent per-rank host arrays; chunked H2D / scan(init=carry) / D2H pipeline"}
+        del hf, hu, of, ou, pipe
+
+    line = None
+    if rank == 0:
+        from oracle import oracle as O
+        cpu = cpu_baseline_object(O.max_threads(), 1 << 26)
+        prim = primitives_table(kf, torch, peak) if (args.detail and world == 1) else None
+        line = {
+            "metric": "effective GB/s, inclusive scan(+), Float32 + UInt32 at n=2^28 per GPU", "value": round(value, 1),
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32+u32", "data": "synthetic",
+            "frac_of_measured_peak": round(value / (peak * world), 4),
+            "frac_of_nominal_8TBs": round(value / (NOMINAL_HBM_GBS * world), 4),
+            "config": {"workload": "inclusive scan!(+, dst, x): Float32 x~U[0,1) n=2^28 and UInt32 x~U{0..255} n=2^28 "
+                                   "per GPU" + ("" if world == 1 else "; sharded over %d GPUs (global n=%d*2^28): local "
+                                                "reduce, NCCL allgather of shard totals, seeded local scan" % (world, world)),
+                       "n_per_gpu": n, "algorithmic_bytes_per_step": step_bytes,
+                       "l2": "inputs (1 GiB per array) are larger than the 126 MB L2; no flush needed"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if prim is not None:
+            line["primitives"] = prim
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--detail", type=int, default=1, help="1: also measure the other primitives (single GPU)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

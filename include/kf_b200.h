@@ -1,0 +1,209 @@
+/*
+ * kf_b200.h — C ABI of libkf_b200.so: hand-written sm_100a kernels for the memory-bound
+ * primitive core of KernelForge.jl (full mapreduce, inclusive scan, radix onesweep sort).
+ *
+ * Conventions shared by every entry point
+ *   - All data pointers are DEVICE pointers, element-aligned only (views are fine).
+ *   - The library never allocates or frees device memory: the caller passes a workspace
+ *     (`ws`, `ws_bytes`) sized by the matching `*_workspace_bytes` query. A workspace can be
+ *     reused across calls on the same stream; the callee re-initialises what it needs.
+ *   - Every entry point is asynchronous on `stream` and returns a `kf_status` (0 = OK) for
+ *     errors the host can see. Errors the device detects (a bounded wait that ran out) land in
+ *     a status word inside the workspace and are read back by `kf_check`.
+ *   - `cfg == NULL` selects the launch parameters from the built-in B200 launch table.
+ *   - Indices are 0-based. Sizes are element counts (`uint64_t`).
+ *
+ * Each declaration cites the reference interface (file:line inside KernelForge.jl v0.2.0) that it
+ * replaces.
+ */
+#ifndef KF_B200_H
+#define KF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KF_B200_ABI_VERSION 1
+
+/* CUDA stream handle (a `cudaStream_t` / `CUstream`); NULL = the legacy default stream. */
+typedef struct CUstream_st *kf_stream_t;
+
+typedef enum kf_status {
+    KF_OK = 0,
+    KF_ERR_INVALID_ARG = 1,        /* null pointer, bad enum, length mismatch */
+    KF_ERR_UNSUPPORTED = 2,        /* (f, op, dtype) or launch override outside the compiled set */
+    KF_ERR_WORKSPACE_TOO_SMALL = 3,
+    KF_ERR_LAUNCH_FAILED = 4,      /* a CUDA runtime call failed; see kf_last_cuda_error() */
+    KF_ERR_TIMEOUT = 5,            /* a bounded device-side wait ran out (reported by kf_check) */
+    KF_ERR_EMPTY_REDUCTION = 6     /* mapreduce over n == 0 has no value (no init element) */
+} kf_status;
+
+/* Element types: the reference's BitwiseTypes (src/KernelForge.jl:15) without Float16. */
+typedef enum kf_dtype {
+    KF_U8 = 0, KF_I8 = 1, KF_U16 = 2, KF_I16 = 3, KF_U32 = 4, KF_I32 = 5,
+    KF_U64 = 6, KF_I64 = 7, KF_F32 = 8, KF_F64 = 9
+} kf_dtype;
+
+/* Element-wise map `f` applied on load (closures the Julia layer recognises by identity). */
+typedef enum kf_map {
+    KF_MAP_IDENTITY = 0,
+    KF_MAP_ABS2 = 1,               /* x*x */
+    KF_MAP_ABS = 2
+} kf_map;
+
+/* Binary operator `op`. KF_OP_AFFINE is the non-commutative composition of affine maps
+ * (a1,b1) o (a2,b2) = (a1*a2, a2*b1 + b2), i.e. "apply the left map, then the right one". */
+typedef enum kf_op {
+    KF_OP_ADD = 0, KF_OP_MUL = 1, KF_OP_MIN = 2, KF_OP_MAX = 3,
+    KF_OP_AND = 4, KF_OP_OR = 5, KF_OP_XOR = 6,
+    KF_OP_AFFINE = 7
+} kf_op;
+
+/* Post-map `g`: applied once to the final value (mapreduce). */
+typedef enum kf_post {
+    KF_POST_IDENTITY = 0,
+    KF_POST_SQRT = 1
+} kf_post;
+
+/* Primitive ids for the launch table. */
+typedef enum kf_primitive {
+    KF_PRIM_MAPREDUCE = 0,
+    KF_PRIM_SCAN = 1,
+    KF_PRIM_SORT_KEYS = 2,
+    KF_PRIM_SORT_PAIRS = 3
+} kf_primitive;
+
+/*
+ * Optional launch override; replaces the reference's per-call kwargs `workgroup`, `Nitem`,
+ * `blocks` (src/mapreduce/1D/mapreduce1d.jl:186-196, src/scan/scan.jl:261-271,
+ * src/sort/sort1d.jl:337-347). A field left 0 is taken from the launch table. Only the
+ * compiled (threads, items) pairs are accepted; anything else returns KF_ERR_UNSUPPORTED.
+ *   threads : CTA size.
+ *   items   : mapreduce/scan: 16-byte vectors per thread per tile; sort: keys per thread.
+ *   blocks  : mapreduce only: number of persistent CTAs.
+ */
+typedef struct kf_launch_cfg {
+    int32_t threads;
+    int32_t items;
+    int32_t blocks;
+    int32_t reserved;
+} kf_launch_cfg;
+
+/* ---- library / errors ---------------------------------------------------------------------- */
+
+/* ABI version of the loaded library (== KF_B200_ABI_VERSION it was built with). */
+int32_t kf_abi_version(void);
+
+/* Human-readable text for a kf_status. Replaces the reference's Julia exceptions
+ * (e.g. src/sort/sort1d.jl:348-349,367-389). */
+const char *kf_error_string(int32_t status);
+
+/* The CUDA runtime error code behind the calling thread's last KF_ERR_LAUNCH_FAILED (0 if none). */
+int32_t kf_last_cuda_error(void);
+
+/* Reads the device-side status word of a workspace after synchronising `stream`.
+ * Returns KF_OK or the error a kernel recorded (KF_ERR_TIMEOUT). The reference has no
+ * counterpart: its look-back spins are unbounded (src/scan/scan_kernel.jl:388-415). */
+int32_t kf_check(const void *ws, kf_stream_t stream);
+
+/* The launch table entry for (primitive, element size in bytes, n). Replaces the generated
+ * `default_*` overrides loaded by src/tuning/loader.jl:93-130 from data/tuning/<Arch>_inline.jl. */
+int32_t kf_launch_table_lookup(int32_t primitive, int32_t elem_bytes, uint64_t n, kf_launch_cfg *out);
+
+/* Number of SMs of the current device. Replaces `num_sms` (ext/KernelForgeCUDAExt.jl:31-33). */
+int32_t kf_num_sms(void);
+
+/* ---- mapreduce ----------------------------------------------------------------------------- */
+
+/* Workspace for kf_mapreduce. Replaces get_allocation(MapReduce1D, ...)
+ * (src/mapreduce/1D/mapreduce1d.jl:140-170): per-CTA partials + a completion counter. */
+size_t kf_mapreduce_workspace_bytes(int32_t dtype, uint64_t n, const kf_launch_cfg *cfg);
+
+/* dst[0] = g(op-reduce_i f(src[i])), i in [0, n). `op` must be associative and commutative
+ * (KF_OP_AFFINE is rejected). Accumulates in the element type, like the reference
+ * (H = promote_op(f, T), src/mapreduce/1D/mapreduce1d_kernel.jl:1-3). One kernel launch; the
+ * last CTA to finish folds the per-CTA partials in index order, so the result is
+ * deterministic for a given launch configuration.
+ * Replaces mapreduce1d! / _mapreduce1d_impl! (src/mapreduce/1D/mapreduce1d.jl:259-346) and
+ * mapreduce1d_kernel! (src/mapreduce/1D/mapreduce1d_kernel.jl:5-94). n == 0 returns
+ * KF_ERR_EMPTY_REDUCTION. */
+int32_t kf_mapreduce(int32_t f, int32_t op, int32_t g, int32_t dtype,
+                     const void *src, uint64_t n, void *dst,
+                     void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
+/* ---- scan ---------------------------------------------------------------------------------- */
+
+/* Workspace for kf_scan / kf_scan_affine_*. Replaces get_allocation(Scan1D, ...)
+ * (src/scan/scan.jl:156-211): one tile descriptor per tile + a tile ticket. `dtype` is the
+ * element type; pass KF_F32 with `pair = 1` for the affine (a, b) pair. */
+size_t kf_scan_workspace_bytes(int32_t dtype, int32_t pair, uint64_t n, const kf_launch_cfg *cfg);
+
+/* Inclusive scan: dst[i] = [init op] f(src[0]) op ... op f(src[i]). Single pass, decoupled
+ * look-back over tile descriptors in the workspace; operand order is preserved.
+ * `init` (device pointer to one element, may be NULL) is folded in from the left; it is how a
+ * sharded scan seeds a shard with the carry of the shards before it.
+ * `dst == src` is allowed. n == 0 is a no-op (src/scan/scan.jl:273).
+ * Replaces scan! / _scan_impl! (src/scan/scan.jl:261-284,414-479) and scan_kernel_packed! /
+ * scan_kernel! (src/scan/scan_kernel.jl:310-478,94-299). */
+int32_t kf_scan(int32_t f, int32_t op, int32_t dtype,
+                const void *src, void *dst, uint64_t n, const void *init,
+                void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
+/* Inclusive scan of affine maps x -> a*x + b under composition (KF_OP_AFFINE), Float32,
+ * structure-of-arrays: (a_dst[i], b_dst[i]) = (a_0,b_0) o ... o (a_i,b_i). `init_ab` points to
+ * two floats (a, b) or is NULL. In reference terms this is scan!(op, dst, src) over
+ * NTuple{2,Float32} on the split-descriptor kernel (src/scan/scan_kernel.jl:94-299). */
+int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, float *a_dst, float *b_dst,
+                           uint64_t n, const float *init_ab,
+                           void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
+/* Same, array-of-structures: src/dst hold n interleaved (a, b) pairs (NTuple{2,Float32}). */
+int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab,
+                           void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
+/* ---- sort ---------------------------------------------------------------------------------- */
+
+/* Workspace for kf_sort_keys (val_bytes == 0) / kf_sort_pairs (val_bytes in {4, 8}).
+ * Replaces get_allocation(Sort1D, ...) (src/sort/sort1d.jl:237-300): digit histograms, tile
+ * descriptors, tile tickets and the n-element ping-pong scratch (keys, and values if any). */
+size_t kf_sort_workspace_bytes(int32_t key_dtype, int32_t val_bytes, uint64_t n, const kf_launch_cfg *cfg);
+
+/* Stable ascending LSD radix sort, 8-bit digits, one onesweep pass per key byte. Keys are
+ * ordered by the reference's uint_map (src/sort/uint_map.jl:11-35): unsigned = identity,
+ * signed = sign bit flipped, floats = sign-flip / complement (-0.0 before +0.0, NaNs by bit
+ * pattern); the original key bits are what is moved. `dst == src` sorts in place.
+ * Replaces _sort1d_impl! (src/sort/sort1d.jl:780-874), _sort_histograms! (:655-697),
+ * bucket_histogram_kernel! (src/sort/bucket_histogram_kernel.jl:77-145),
+ * scan_histogram_kernel! (src/sort/scan_histogram_kernel.jl:20-46) and the onesweep pass
+ * kernel (src/sort/onesweep_kernel.jl:113-488). n == 0 is a no-op. */
+int32_t kf_sort_keys(int32_t key_dtype, const void *src, void *dst, uint64_t n,
+                     void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
+/* Key-value form: sorts (keys, vals) by key, stable; vals are opaque `val_bytes`-wide payloads.
+ * Replaces _sort1d_keyval_impl! (src/sort/sort1d.jl:1006-1090) and the key-value pass kernel
+ * (src/sort/keyval_onesweep_kernel.jl:45-317). */
+int32_t kf_sort_pairs(int32_t key_dtype, const void *keys_src, void *keys_dst,
+                      int32_t val_bytes, const void *vals_src, void *vals_dst, uint64_t n,
+                      void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
+/* ---- helpers used by the sharded (multi-GPU) layer and by sortperm --------------------------- */
+
+/* dst[i] = start + i (uint32 or uint64 by `dtype`). The iota fill of sortperm!
+ * (src/sort/sortperm.jl:162-214). */
+int32_t kf_iota(int32_t dtype, void *dst, uint64_t n, uint64_t start, kf_stream_t stream);
+
+/* For each of `nsplit` splitters (ascending, same dtype as keys), the index of the first element
+ * of the SORTED array `keys` whose mapped key is greater than the splitter ("upper bound").
+ * out[j] is uint64. Used to cut a sorted shard into per-destination runs for the sample sort;
+ * the reference has no multi-GPU layer, the closest code is the splitter search of
+ * src/sort/sample_sort.jl:284-312. */
+int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t n,
+                        const void *splitters, int32_t nsplit, uint64_t *out, kf_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KF_B200_H */

@@ -1,0 +1,73 @@
+// Library-level entry points: version, error text, device status read-back and the B200 launch
+// table that stands in for the reference's generated per-architecture tuning files.
+#include "common.cuh"
+
+#include "launch_table.h"
+
+namespace kf {
+
+static thread_local int g_last_cuda_error = 0;
+void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = (int)e; }
+
+// SM count of the current device; 148 (B200) when no device can be queried, so that size queries
+// still answer on a machine without a GPU.
+int device_sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    return sms;
+}
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" int32_t kf_abi_version(void) { return KF_B200_ABI_VERSION; }
+
+extern "C" const char *kf_error_string(int32_t status) {
+    switch (status) {
+    case KF_OK: return "ok";
+    case KF_ERR_INVALID_ARG: return "invalid argument (null or misaligned pointer, bad enum, or size out of range)";
+    case KF_ERR_UNSUPPORTED: return "unsupported combination of map, operator, element type or launch override";
+    case KF_ERR_WORKSPACE_TOO_SMALL: return "workspace smaller than the *_workspace_bytes query for these arguments";
+    case KF_ERR_LAUNCH_FAILED: return "a CUDA runtime call failed (see kf_last_cuda_error)";
+    case KF_ERR_TIMEOUT: return "a bounded device-side wait on a tile descriptor ran out";
+    case KF_ERR_EMPTY_REDUCTION: return "reducing over an empty collection is not allowed (no init value)";
+    default: return "unknown kf_status";
+    }
+}
+
+extern "C" int32_t kf_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" int32_t kf_check(const void *ws, kf_stream_t stream) {
+    if (!ws) return KF_ERR_INVALID_ARG;
+    unsigned int status = 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    KF_CUDA_TRY(cudaMemcpyAsync(&status, ws, sizeof(status), cudaMemcpyDeviceToHost, s));
+    KF_CUDA_TRY(cudaStreamSynchronize(s));
+    return (int32_t)status;
+}
+
+extern "C" int32_t kf_num_sms(void) { return device_sm_count(); }
+
+extern "C" int32_t kf_launch_table_lookup(int32_t primitive, int32_t elem_bytes, uint64_t n, kf_launch_cfg *out) {
+    if (!out) return KF_ERR_INVALID_ARG;
+    const LaunchRow *best = nullptr;
+    const uint64_t bytes = n * (uint64_t)(elem_bytes > 0 ? elem_bytes : 1);
+    // First row that matches the primitive and element size and whose bound covers the input.
+    for (int i = 0; i < kNumLaunchRows && !best; ++i) {
+        const LaunchRow &r = kLaunchTable[i];
+        if (r.primitive != primitive) continue;
+        if (r.elem_bytes != 0 && r.elem_bytes != elem_bytes) continue;
+        if (bytes <= r.max_bytes) best = &r;
+    }
+    if (!best) return KF_ERR_UNSUPPORTED;
+    out->threads = best->threads;
+    out->items = best->items;
+    out->blocks = best->blocks_per_sm > 0 ? best->blocks_per_sm * device_sm_count() : 0;
+    out->reserved = 0;
+    return KF_OK;
+}

@@ -1,0 +1,287 @@
+// Shared device/host helpers for the sm_100a kernels: element operators, 128-bit streaming
+// loads/stores, relaxed 64-bit descriptor accesses, bounded waits and the workspace header.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/kf_b200.h"
+
+namespace kf {
+
+typedef unsigned long long u64;
+typedef unsigned int u32;
+
+// ---------------------------------------------------------------------------------------------
+// Workspace header. Every workspace starts with this 256-byte block; the callee clears it (and
+// the descriptors behind it) with one memset at the start of a call.
+//   word 0      : device status (0 = OK, else a kf_status a kernel recorded)
+//   word 1      : where a wait gave up (tile index), for diagnostics
+//   words 8..23 : tile tickets / completion counters (one per kernel launch of the call)
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kHeaderBytes = 256;
+constexpr int kStatusWord = 0;
+constexpr int kStatusAux = 1;
+constexpr int kTicketBase = 8;
+
+// Polls before a waiting tile gives up. Each poll is an L2 round trip (~1 us with back-off), so
+// the limit is on the order of a second; a healthy look-back needs a handful of polls.
+constexpr u32 kSpinLimit = 1u << 20;
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---------------------------------------------------------------------------------------------
+// Raw memory access
+// ---------------------------------------------------------------------------------------------
+
+// 128-bit read-only streaming load: bypasses L1 allocation (data is used once).
+__device__ __forceinline__ uint4 ld_stream_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+// Coherent 128-bit streaming load (used when dst may alias src, where the non-coherent path is
+// not allowed); still skips L1 allocation.
+__device__ __forceinline__ uint4 ld_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+// 128-bit streaming store (evict-first: written once, not read again by this kernel).
+__device__ __forceinline__ void st_stream_v4(void *p, uint4 v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// Relaxed, device-scope 64-bit accesses for tile descriptors. A descriptor carries its own
+// status in the same word as the value, so no fence is needed to pair them.
+__device__ __forceinline__ u64 ld_relaxed_u64(const u64 *p) {
+    u64 v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(u64 *p, u64 v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ u32 ld_relaxed_u32(const u32 *p) {
+    u32 v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ u32 ld_acquire_u32(const u32 *p) {
+    u32 v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ u32 lane_id() {
+    u32 l;
+    asm("mov.u32 %0, %%laneid;" : "=r"(l));
+    return l;
+}
+__device__ __forceinline__ u32 lanemask_lt() {
+    u32 m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
+}
+
+// Records a device-side error once (first writer wins) in the workspace header.
+__device__ __forceinline__ void record_error(u32 *header, int code, u32 where) {
+    if (atomicCAS(&header[kStatusWord], 0u, (u32)code) == 0u) header[kStatusAux] = where;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Element operators. `apply(l, r)` combines an EARLIER value `l` with a LATER value `r`.
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Limits;
+template <> struct Limits<uint8_t> { static __host__ __device__ uint8_t lo() { return 0; } static __host__ __device__ uint8_t hi() { return 0xFF; } };
+template <> struct Limits<int8_t> { static __host__ __device__ int8_t lo() { return -128; } static __host__ __device__ int8_t hi() { return 127; } };
+template <> struct Limits<uint16_t> { static __host__ __device__ uint16_t lo() { return 0; } static __host__ __device__ uint16_t hi() { return 0xFFFF; } };
+template <> struct Limits<int16_t> { static __host__ __device__ int16_t lo() { return -32768; } static __host__ __device__ int16_t hi() { return 32767; } };
+template <> struct Limits<uint32_t> { static __host__ __device__ uint32_t lo() { return 0; } static __host__ __device__ uint32_t hi() { return 0xFFFFFFFFu; } };
+template <> struct Limits<int32_t> { static __host__ __device__ int32_t lo() { return INT32_MIN; } static __host__ __device__ int32_t hi() { return INT32_MAX; } };
+template <> struct Limits<u64> { static __host__ __device__ u64 lo() { return 0; } static __host__ __device__ u64 hi() { return ~0ull; } };
+template <> struct Limits<long long> { static __host__ __device__ long long lo() { return INT64_MIN; } static __host__ __device__ long long hi() { return INT64_MAX; } };
+template <> struct Limits<float> {
+    static __host__ __device__ float lo() { return -__builtin_huge_valf(); }
+    static __host__ __device__ float hi() { return __builtin_huge_valf(); }
+};
+template <> struct Limits<double> {
+    static __host__ __device__ double lo() { return -__builtin_huge_val(); }
+    static __host__ __device__ double hi() { return __builtin_huge_val(); }
+};
+
+template <typename T> struct IsFloat { static constexpr bool value = false; };
+template <> struct IsFloat<float> { static constexpr bool value = true; };
+template <> struct IsFloat<double> { static constexpr bool value = true; };
+
+struct OpAdd {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l + r); }
+    // -0.0 is the exact additive identity of IEEE floats (+0.0 would turn a leading -0.0 into +0.0).
+    template <typename T> static __device__ __forceinline__ T identity() {
+        if constexpr (IsFloat<T>::value) return (T)-0.0;
+        else return (T)0;
+    }
+};
+struct OpMul {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l * r); }
+    template <typename T> static __device__ __forceinline__ T identity() { return (T)1; }
+};
+struct OpMin {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return r < l ? r : l; }
+    template <typename T> static __device__ __forceinline__ T identity() { return Limits<T>::hi(); }
+};
+struct OpMax {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return l < r ? r : l; }
+    template <typename T> static __device__ __forceinline__ T identity() { return Limits<T>::lo(); }
+};
+struct OpAnd {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l & r); }
+    template <typename T> static __device__ __forceinline__ T identity() { return (T)~(T)0; }
+};
+struct OpOr {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l | r); }
+    template <typename T> static __device__ __forceinline__ T identity() { return (T)0; }
+};
+struct OpXor {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l ^ r); }
+    template <typename T> static __device__ __forceinline__ T identity() { return (T)0; }
+};
+
+// An affine map x -> a*x + b. Composition applies the left map first:
+// (a1,b1) o (a2,b2) = (a1*a2, a2*b1 + b2). The b component is one fused multiply-add (a single
+// rounding), which is at least as close to the Float64 left fold as separate mul and add.
+struct Affine {
+    float a, b;
+};
+struct OpAffine {
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) {
+        T o;
+        o.a = l.a * r.a;
+        o.b = fmaf(r.a, l.b, r.b);
+        return o;
+    }
+    template <typename T> static __device__ __forceinline__ T identity() {
+        T o;
+        o.a = 1.0f;
+        o.b = -0.0f;
+        return o;
+    }
+};
+
+// Element-wise map f, selected at run time (uniform across the grid; the kernels are
+// HBM-bound, the branch is free).
+template <typename T> __device__ __forceinline__ T apply_map(int f, T x) {
+    if (f == KF_MAP_ABS2) return (T)(x * x);
+    if (f == KF_MAP_ABS) return x < (T)0 ? (T)(0 - x) : x;  // integers: wraps at the minimum, like Julia
+    return x;
+}
+template <> __device__ __forceinline__ float apply_map<float>(int f, float x) {
+    if (f == KF_MAP_ABS2) return x * x;
+    if (f == KF_MAP_ABS) return fabsf(x);
+    return x;
+}
+template <> __device__ __forceinline__ double apply_map<double>(int f, double x) {
+    if (f == KF_MAP_ABS2) return x * x;
+    if (f == KF_MAP_ABS) return fabs(x);
+    return x;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Warp shuffles for any 4- or 8-byte trivially copyable type.
+// ---------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ T shfl_up(T v, int d) {
+    if constexpr (sizeof(T) == 8) {
+        u64 x;
+        memcpy(&x, &v, 8);
+        x = __shfl_up_sync(0xFFFFFFFFu, x, d);
+        T o;
+        memcpy(&o, &x, 8);
+        return o;
+    } else {
+        static_assert(sizeof(T) <= 4, "unsupported shuffle width");
+        u32 x = 0;
+        memcpy(&x, &v, sizeof(T));
+        x = __shfl_up_sync(0xFFFFFFFFu, x, d);
+        T o;
+        memcpy(&o, &x, sizeof(T));
+        return o;
+    }
+}
+template <typename T> __device__ __forceinline__ T shfl_down(T v, int d) {
+    if constexpr (sizeof(T) == 8) {
+        u64 x;
+        memcpy(&x, &v, 8);
+        x = __shfl_down_sync(0xFFFFFFFFu, x, d);
+        T o;
+        memcpy(&o, &x, 8);
+        return o;
+    } else {
+        u32 x = 0;
+        memcpy(&x, &v, sizeof(T));
+        x = __shfl_down_sync(0xFFFFFFFFu, x, d);
+        T o;
+        memcpy(&o, &x, sizeof(T));
+        return o;
+    }
+}
+template <typename T> __device__ __forceinline__ T shfl_idx(T v, int src) {
+    if constexpr (sizeof(T) == 8) {
+        u64 x;
+        memcpy(&x, &v, 8);
+        x = __shfl_sync(0xFFFFFFFFu, x, src);
+        T o;
+        memcpy(&o, &x, 8);
+        return o;
+    } else {
+        u32 x = 0;
+        memcpy(&x, &v, sizeof(T));
+        x = __shfl_sync(0xFFFFFFFFu, x, src);
+        T o;
+        memcpy(&o, &x, sizeof(T));
+        return o;
+    }
+}
+
+// Inclusive warp scan that keeps operand order (lane i holds x_0 op ... op x_i).
+template <typename Op, typename T> __device__ __forceinline__ T warp_scan_inclusive(T v, u32 lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        T up = shfl_up(v, d);
+        if (lane >= (u32)d) v = Op::template apply<T>(up, v);
+    }
+    return v;
+}
+
+// Host-side dtype size.
+inline int dtype_bytes(int dtype) {
+    switch (dtype) {
+    case KF_U8: case KF_I8: return 1;
+    case KF_U16: case KF_I16: return 2;
+    case KF_U32: case KF_I32: case KF_F32: return 4;
+    case KF_U64: case KF_I64: case KF_F64: return 8;
+    default: return 0;
+    }
+}
+
+// Host: remembers the CUDA error behind the last KF_ERR_LAUNCH_FAILED of this thread.
+void set_last_cuda_error(cudaError_t e);
+
+#define KF_CUDA_TRY(expr)                                   \
+    do {                                                    \
+        cudaError_t _e = (expr);                            \
+        if (_e != cudaSuccess) {                            \
+            ::kf::set_last_cuda_error(_e);                  \
+            return KF_ERR_LAUNCH_FAILED;                    \
+        }                                                   \
+    } while (0)
+
+int device_sm_count();
+
+}  // namespace kf

@@ -1,0 +1,149 @@
+// Host entry points of the inclusive scan (C ABI): launch geometry, workspace layout, dtype dispatch.
+// The kernels live in scan_impl.cuh and are instantiated per element type in scan_inst_*.cu.
+#include "scan_impl.cuh"
+
+namespace kf {
+
+int scan_plan(int elem_bytes, int epv, u64 n, const kf_launch_cfg *cfg, ScanPlan *plan) {
+    kf_launch_cfg t;
+    kf_launch_table_lookup(KF_PRIM_SCAN, elem_bytes, n, &t);
+    if (cfg) {
+        if (cfg->threads) t.threads = cfg->threads;
+        if (cfg->items) t.items = cfg->items;
+    }
+    int v = -1;
+    for (int i = 0; i < kNumScanVariants; ++i)
+        if (kScanVariants[i].threads == t.threads && kScanVariants[i].vecs == t.items) v = i;
+    if (v < 0) return KF_ERR_UNSUPPORTED;
+    plan->variant = v;
+    plan->tile = (u64)t.threads * t.items * epv;
+    plan->ntiles = 1 + (n + plan->tile - 1) / plan->tile;  // +1: a possible short head tile
+    plan->words = elem_bytes <= 4 ? 1 : 2;
+    if (plan->ntiles >= (1ull << 31)) return KF_ERR_INVALID_ARG;
+    return KF_OK;
+}
+
+static size_t scan_ws_bytes(const ScanPlan &p) { return kHeaderBytes + align_up(p.ntiles * p.words * 8, 256); }
+
+// Fills the geometry that depends on the actual pointers: the shared 16-byte misalignment (if
+// any) becomes a short head tile, otherwise every tile takes the element-wise path.
+static void scan_geometry(const ScanPlan &p, u64 n, int elem_bytes, const uintptr_t *ptrs, int nptrs,
+                          ScanArgs *a) {
+    const uintptr_t mis = ptrs[0] & 15u;
+    bool same = (mis % elem_bytes) == 0;
+    for (int i = 1; i < nptrs; ++i) same = same && ((ptrs[i] & 15u) == mis);
+    u64 head = 0;
+    if (same && mis) head = (16 - mis) / elem_bytes;
+    if (head > n) head = n;
+    a->n = n;
+    a->vec_ok = same ? 1 : 0;
+    a->head = same ? head : 0;
+    const u64 first = a->head > 0 ? 1 : 0;
+    a->ntiles = first + (n - a->head + p.tile - 1) / p.tile;
+}
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" size_t kf_scan_workspace_bytes(int32_t dtype, int32_t pair, uint64_t n, const kf_launch_cfg *cfg) {
+    const int eb = pair ? 8 : dtype_bytes(dtype);
+    if (eb == 0 || (pair && dtype != KF_F32)) return 0;
+    ScanPlan p;
+    // The two-array affine layout packs 4 pairs per slot, the other layouts 16/elem_bytes
+    // elements; size for the smaller tile (more tiles) so one workspace fits both layouts.
+    if (scan_plan(eb, 16 / eb, n, cfg, &p) != KF_OK) return 0;
+    return scan_ws_bytes(p);
+}
+
+extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t dtype, const void *src, void *dst, uint64_t n,
+                           const void *init, void *ws, size_t ws_bytes, const kf_launch_cfg *cfg,
+                           kf_stream_t stream) {
+    const int eb = dtype_bytes(dtype);
+    if (eb == 0) return KF_ERR_INVALID_ARG;
+    if (f < KF_MAP_IDENTITY || f > KF_MAP_ABS) return KF_ERR_UNSUPPORTED;
+    if (op < KF_OP_ADD || op > KF_OP_XOR) return KF_ERR_UNSUPPORTED;
+    if (n == 0) return KF_OK;
+    if (!src || !dst || !ws) return KF_ERR_INVALID_ARG;
+    if (((uintptr_t)src % eb) || ((uintptr_t)dst % eb) || ((uintptr_t)ws % 256) || (init && ((uintptr_t)init % eb)))
+        return KF_ERR_INVALID_ARG;
+    ScanPlan p;
+    int rc = scan_plan(eb, 16 / eb, n, cfg, &p);
+    if (rc != KF_OK) return rc;
+    if (ws_bytes < scan_ws_bytes(p)) return KF_ERR_WORKSPACE_TOO_SMALL;
+
+    ScanArgs a;
+    const uintptr_t ptrs[2] = {(uintptr_t)src, (uintptr_t)dst};
+    scan_geometry(p, n, eb, ptrs, 2, &a);
+    a.header = (u32 *)ws;
+    a.desc = (u64 *)((char *)ws + kHeaderBytes);
+    a.init = init;
+    a.f = f;
+    cudaStream_t s = (cudaStream_t)stream;
+    KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
+    switch (dtype) {
+    case KF_U8: return scan_dispatch_u8(op, p.variant, src, dst, a, s);
+    case KF_I8: return scan_dispatch_i8(op, p.variant, src, dst, a, s);
+    case KF_U16: return scan_dispatch_u16(op, p.variant, src, dst, a, s);
+    case KF_I16: return scan_dispatch_i16(op, p.variant, src, dst, a, s);
+    case KF_U32: return scan_dispatch_u32(op, p.variant, src, dst, a, s);
+    case KF_I32: return scan_dispatch_i32(op, p.variant, src, dst, a, s);
+    case KF_U64: return scan_dispatch_u64(op, p.variant, src, dst, a, s);
+    case KF_I64: return scan_dispatch_i64(op, p.variant, src, dst, a, s);
+    case KF_F32: return scan_dispatch_f32(op, p.variant, src, dst, a, s);
+    case KF_F64: return scan_dispatch_f64(op, p.variant, src, dst, a, s);
+    default: return KF_ERR_INVALID_ARG;
+    }
+}
+
+extern "C" int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, float *a_dst, float *b_dst,
+                                      uint64_t n, const float *init_ab, void *ws, size_t ws_bytes,
+                                      const kf_launch_cfg *cfg, kf_stream_t stream) {
+    if (n == 0) return KF_OK;
+    if (!a_src || !b_src || !a_dst || !b_dst || !ws) return KF_ERR_INVALID_ARG;
+    const uintptr_t ptrs[4] = {(uintptr_t)a_src, (uintptr_t)b_src, (uintptr_t)a_dst, (uintptr_t)b_dst};
+    for (int i = 0; i < 4; ++i)
+        if (ptrs[i] % 4) return KF_ERR_INVALID_ARG;
+    if (((uintptr_t)ws % 256) || (init_ab && ((uintptr_t)init_ab % 4))) return KF_ERR_INVALID_ARG;
+    ScanPlan p, psize;
+    int rc = scan_plan(8, 4, n, cfg, &p);
+    if (rc != KF_OK) return rc;
+    rc = scan_plan(8, 2, n, cfg, &psize);  // the size kf_scan_workspace_bytes reports
+    if (rc != KF_OK) return rc;
+    if (ws_bytes < scan_ws_bytes(p)) return KF_ERR_WORKSPACE_TOO_SMALL;
+    (void)psize;
+
+    ScanArgs a;
+    scan_geometry(p, n, 4, ptrs, 4, &a);
+    a.header = (u32 *)ws;
+    a.desc = (u64 *)((char *)ws + kHeaderBytes);
+    a.init = init_ab;
+    a.f = KF_MAP_IDENTITY;
+    cudaStream_t s = (cudaStream_t)stream;
+    KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
+    return scan_dispatch_affine_soa(p.variant, a_src, b_src, a_dst, b_dst, a, s);
+}
+
+extern "C" int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab,
+                                      void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream) {
+    if (n == 0) return KF_OK;
+    if (!ab_src || !ab_dst || !ws) return KF_ERR_INVALID_ARG;
+    if (((uintptr_t)ab_src % 4) || ((uintptr_t)ab_dst % 4) || ((uintptr_t)ws % 256) ||
+        (init_ab && ((uintptr_t)init_ab % 4)))
+        return KF_ERR_INVALID_ARG;
+    ScanPlan p;
+    int rc = scan_plan(8, 2, n, cfg, &p);
+    if (rc != KF_OK) return rc;
+    if (ws_bytes < scan_ws_bytes(p)) return KF_ERR_WORKSPACE_TOO_SMALL;
+
+    ScanArgs a;
+    const uintptr_t ptrs[2] = {(uintptr_t)ab_src, (uintptr_t)ab_dst};
+    scan_geometry(p, n, 8, ptrs, 2, &a);
+    a.header = (u32 *)ws;
+    a.desc = (u64 *)((char *)ws + kHeaderBytes);
+    a.init = init_ab;
+    a.f = KF_MAP_IDENTITY;
+    cudaStream_t s = (cudaStream_t)stream;
+    KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
+    return scan_dispatch_affine_aos(p.variant, ab_src, ab_dst, a, s);
+}

@@ -1,0 +1,222 @@
+// Host entry points of the radix onesweep sort (C ABI): workspace layout, ping-pong plan, pass loop.
+// The kernels live in sort_impl.cuh and are instantiated per key width in sort_inst_*.cu.
+#include "sort_impl.cuh"
+
+namespace kf {
+
+__global__ void sort_scan_histogram_kernel(u64 *ghist) {
+    __shared__ u64 s_warp[kRadix / 32];
+    u64 *h = ghist + (size_t)blockIdx.x * kRadix;
+    const u32 tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const u64 c = h[tid];
+    u64 incl = c;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const u64 up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= (u32)d) incl += up;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    u64 base = 0;
+    for (u32 w = 0; w < warp; ++w) base += s_warp[w];
+    h[tid] = base + incl - c;
+}
+
+struct KeyInfo {
+    int bytes;
+    bool is_float;
+    bool signed_or_float;
+};
+static bool key_info(int dtype, KeyInfo *k) {
+    switch (dtype) {
+    case KF_U32: *k = {4, false, false}; return true;
+    case KF_I32: *k = {4, false, true}; return true;
+    case KF_F32: *k = {4, true, true}; return true;
+    case KF_U64: *k = {8, false, false}; return true;
+    case KF_I64: *k = {8, false, true}; return true;
+    case KF_F64: *k = {8, true, true}; return true;
+    default: return false;
+    }
+}
+
+struct SortPlan {
+    int variant;
+    u64 tile, ntiles;
+    size_t off_hist, off_desc, off_keys, off_vals, clear_bytes, total;
+};
+
+static int sort_plan(const KeyInfo &k, int val_bytes, u64 n, const kf_launch_cfg *cfg, SortPlan *p) {
+    kf_launch_cfg t;
+    kf_launch_table_lookup(val_bytes ? KF_PRIM_SORT_PAIRS : KF_PRIM_SORT_KEYS, k.bytes + val_bytes, n, &t);
+    if (cfg) {
+        if (cfg->threads) t.threads = cfg->threads;
+        if (cfg->items) t.items = cfg->items;
+    }
+    int v = -1;
+    for (int i = 0; i < kNumSortVariants; ++i)
+        if (kSortVariants[i].threads == t.threads && kSortVariants[i].items == t.items) v = i;
+    if (v < 0) return KF_ERR_UNSUPPORTED;
+    // Shared memory of the variant: digit counters per warp + the staged tile.
+    const size_t smem = (size_t)(t.threads / 32) * kRadix * 4 + kRadix * 8 +
+                        (size_t)t.threads * t.items * (k.bytes + val_bytes) + 64;
+    if (smem > 227 * 1024) return KF_ERR_UNSUPPORTED;
+    p->variant = v;
+    p->tile = (u64)t.threads * t.items;
+    p->ntiles = (n + p->tile - 1) / p->tile;
+    if (p->ntiles >= (1ull << 31)) return KF_ERR_INVALID_ARG;
+    p->off_hist = kHeaderBytes;
+    p->off_desc = p->off_hist + align_up((size_t)k.bytes * kRadix * 8, 256);
+    p->clear_bytes = p->off_desc + p->ntiles * kRadix * 8;
+    p->off_keys = align_up(p->clear_bytes, 256);
+    p->off_vals = p->off_keys + align_up(n * k.bytes, 256);
+    p->total = p->off_vals + align_up(n * val_bytes, 256);
+    return KF_OK;
+}
+
+static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val_bytes, const void *vals_src,
+                    void *vals_dst, u64 n, void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, cudaStream_t s) {
+    KeyInfo k;
+    if (!key_info(key_dtype, &k)) return dtype_bytes(key_dtype) ? KF_ERR_UNSUPPORTED : KF_ERR_INVALID_ARG;
+    if (val_bytes != 0 && val_bytes != 4 && val_bytes != 8) return KF_ERR_UNSUPPORTED;
+    if (n == 0) return KF_OK;
+    if (!keys_src || !keys_dst || !ws) return KF_ERR_INVALID_ARG;
+    if (val_bytes && (!vals_src || !vals_dst)) return KF_ERR_INVALID_ARG;
+    if (((uintptr_t)keys_src % k.bytes) || ((uintptr_t)keys_dst % k.bytes) || ((uintptr_t)ws % 256))
+        return KF_ERR_INVALID_ARG;
+    if (val_bytes && (((uintptr_t)vals_src % val_bytes) || ((uintptr_t)vals_dst % val_bytes)))
+        return KF_ERR_INVALID_ARG;
+    SortPlan p;
+    int rc = sort_plan(k, val_bytes, n, cfg, &p);
+    if (rc != KF_OK) return rc;
+    if (ws_bytes < p.total) return KF_ERR_WORKSPACE_TOO_SMALL;
+
+    char *base = (char *)ws;
+    u32 *header = (u32 *)base;
+    u64 *ghist = (u64 *)(base + p.off_hist);
+    u64 *desc = (u64 *)(base + p.off_desc);
+    void *kscratch = base + p.off_keys;
+    void *vscratch = base + p.off_vals;
+
+    KF_CUDA_TRY(cudaMemsetAsync(ws, 0, p.clear_bytes, s));
+    rc = k.bytes == 4 ? sort_hist_k32(k.is_float, keys_src, n, ghist, k.signed_or_float, s)
+                      : sort_hist_k64(k.is_float, keys_src, n, ghist, k.signed_or_float, s);
+    if (rc != KF_OK) return rc;
+    sort_scan_histogram_kernel<<<k.bytes, kRadix, 0, s>>>(ghist);
+    KF_CUDA_TRY(cudaGetLastError());
+
+    // Ping-pong plan: pass p writes dst when the number of passes still to come is even, else the
+    // scratch; pass 0 reads src. With an even pass count this never writes src unless dst == src,
+    // and the last pass always lands in dst.
+    const int P = k.bytes;
+    const void *kin = keys_src, *vin = vals_src;
+    for (int pass = 0; pass < P; ++pass) {
+        const bool to_dst = ((P - 1 - pass) % 2) == 0;
+        void *kout = to_dst ? keys_dst : kscratch;
+        void *vout = to_dst ? vals_dst : vscratch;
+        SortPassArgs a;
+        a.keys_in = kin;
+        a.keys_out = kout;
+        a.vals_in = vin;
+        a.vals_out = vout;
+        a.n = n;
+        a.ntiles = p.ntiles;
+        a.gexcl = ghist + (size_t)pass * kRadix;
+        a.desc = desc;
+        a.header = header;
+        a.pass = pass;
+        a.shift = 8 * pass;
+        a.top_xor = (pass == P - 1 && k.signed_or_float) ? 0x80u : 0u;
+        a.signed_or_float = k.signed_or_float;
+        rc = k.bytes == 4 ? sort_pass_k32(k.is_float, val_bytes, p.variant, a, s)
+                          : sort_pass_k64(k.is_float, val_bytes, p.variant, a, s);
+        if (rc != KF_OK) return rc;
+        kin = kout;
+        vin = vout;
+    }
+    return KF_OK;
+}
+
+// ---- small helpers of the sharded layer ---------------------------------------------------------
+template <typename T> __global__ void iota_kernel(T *dst, u64 n, u64 start) {
+    const u64 stride = (u64)gridDim.x * blockDim.x;
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = (T)(start + i);
+}
+
+// Order-preserving unsigned image of a key (the reference's uint_map).
+template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT mapped_key(KeyT k, bool sof) {
+    const KeyT sign = (KeyT)1 << (8 * sizeof(KeyT) - 1);
+    return radix_bits<KeyT, IS_FLOAT>(k) ^ (sof ? sign : (KeyT)0);
+}
+
+template <typename KeyT, bool IS_FLOAT>
+__global__ void upper_bounds_kernel(const KeyT *keys, u64 n, const KeyT *splitters, int nsplit, u64 *out, bool sof) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= nsplit) return;
+    const KeyT s = mapped_key<KeyT, IS_FLOAT>(splitters[j], sof);
+    u64 lo = 0, hi = n;  // first index whose mapped key is > s
+    while (lo < hi) {
+        const u64 mid = lo + (hi - lo) / 2;
+        if (mapped_key<KeyT, IS_FLOAT>(keys[mid], sof) <= s) lo = mid + 1;
+        else hi = mid;
+    }
+    out[j] = lo;
+}
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" size_t kf_sort_workspace_bytes(int32_t key_dtype, int32_t val_bytes, uint64_t n, const kf_launch_cfg *cfg) {
+    KeyInfo k;
+    if (!key_info(key_dtype, &k)) return 0;
+    if (val_bytes != 0 && val_bytes != 4 && val_bytes != 8) return 0;
+    SortPlan p;
+    if (sort_plan(k, val_bytes, n, cfg, &p) != KF_OK) return 0;
+    return p.total;
+}
+
+extern "C" int32_t kf_sort_keys(int32_t key_dtype, const void *src, void *dst, uint64_t n, void *ws,
+                                size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream) {
+    return sort_run(key_dtype, src, dst, 0, nullptr, nullptr, n, ws, ws_bytes, cfg, (cudaStream_t)stream);
+}
+
+extern "C" int32_t kf_sort_pairs(int32_t key_dtype, const void *keys_src, void *keys_dst, int32_t val_bytes,
+                                 const void *vals_src, void *vals_dst, uint64_t n, void *ws, size_t ws_bytes,
+                                 const kf_launch_cfg *cfg, kf_stream_t stream) {
+    if (val_bytes == 0) return KF_ERR_INVALID_ARG;
+    return sort_run(key_dtype, keys_src, keys_dst, val_bytes, vals_src, vals_dst, n, ws, ws_bytes, cfg,
+                    (cudaStream_t)stream);
+}
+
+extern "C" int32_t kf_iota(int32_t dtype, void *dst, uint64_t n, uint64_t start, kf_stream_t stream) {
+    if (n == 0) return KF_OK;
+    if (!dst) return KF_ERR_INVALID_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    u64 blocks = (n + 1023) / 1024;
+    const u64 cap = (u64)device_sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (dtype == KF_U32 || dtype == KF_I32) iota_kernel<uint32_t><<<(unsigned)blocks, 256, 0, s>>>((uint32_t *)dst, n, start);
+    else if (dtype == KF_U64 || dtype == KF_I64) iota_kernel<u64><<<(unsigned)blocks, 256, 0, s>>>((u64 *)dst, n, start);
+    else return KF_ERR_UNSUPPORTED;
+    KF_CUDA_TRY(cudaGetLastError());
+    return KF_OK;
+}
+
+extern "C" int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t n, const void *splitters,
+                                   int32_t nsplit, uint64_t *out, kf_stream_t stream) {
+    KeyInfo k;
+    if (!key_info(key_dtype, &k)) return KF_ERR_UNSUPPORTED;
+    if (nsplit <= 0) return KF_OK;
+    if (!splitters || !out || (n && !keys)) return KF_ERR_INVALID_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 128, blocks = (nsplit + threads - 1) / threads;
+    if (k.bytes == 4) {
+        if (k.is_float) upper_bounds_kernel<uint32_t, true><<<blocks, threads, 0, s>>>((const uint32_t *)keys, n, (const uint32_t *)splitters, nsplit, (u64 *)out, true);
+        else upper_bounds_kernel<uint32_t, false><<<blocks, threads, 0, s>>>((const uint32_t *)keys, n, (const uint32_t *)splitters, nsplit, (u64 *)out, k.signed_or_float);
+    } else {
+        if (k.is_float) upper_bounds_kernel<u64, true><<<blocks, threads, 0, s>>>((const u64 *)keys, n, (const u64 *)splitters, nsplit, (u64 *)out, true);
+        else upper_bounds_kernel<u64, false><<<blocks, threads, 0, s>>>((const u64 *)keys, n, (const u64 *)splitters, nsplit, (u64 *)out, k.signed_or_float);
+    }
+    KF_CUDA_TRY(cudaGetLastError());
+    return KF_OK;
+}

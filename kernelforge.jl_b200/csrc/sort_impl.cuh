@@ -1,0 +1,420 @@
+// Stable LSD radix sort for sm_100a: one fused multi-digit histogram pass, then one "onesweep"
+// pass per key byte (rank inside the tile, decoupled look-back for the per-digit global offsets,
+// scatter staged through shared memory so each digit's run leaves the CTA contiguously).
+//
+// Key order is the reference's uint_map (src/sort/uint_map.jl:11-35 of KernelForge.jl): unsigned
+// keys by value, signed keys with the sign bit flipped, floats sign-flipped when non-negative and
+// complemented when negative. Only digit extraction uses the mapped key; the original bits are
+// what moves. For integer keys the map only changes the top byte, so it costs one XOR folded into
+// the digit mask (`top_xor`); float keys add a shift and one logic op per key for the complement.
+//
+// Ranking uses match.any: all lanes holding the same digit find each other in one instruction, the
+// lowest such lane bumps the warp's private digit counter once for the whole group, and every lane
+// adds the count of lower lanes in its group. Ranks therefore follow element order for any data,
+// which is what makes each pass stable (shared-memory atomics alone would not guarantee it).
+//
+// Tile descriptors are one 64-bit word per (tile, digit): {tag:8 | count:56}. The tag encodes the
+// pass and the state (aggregate / inclusive prefix / poison), so one descriptor array, cleared
+// once per sort call, serves all passes and counts are not limited to 30 bits. Tiles are handed
+// out by an atomic ticket; every wait is bounded.
+#pragma once
+
+#include "common.cuh"
+
+#include <type_traits>
+
+namespace kf {
+
+constexpr int kRadix = 256;
+
+enum : u32 { kStAggregate = 0, kStPrefix = 1, kStPoison = 2 };
+__host__ __device__ __forceinline__ u64 desc_tag(int pass, u32 state) { return (u64)(1 + pass * 3 + (int)state) << 56; }
+constexpr u64 kCountMask = (1ull << 56) - 1;
+
+// Bits of the key that feed digit extraction, before the shift. The sign bit is flipped for every
+// signed or float key, and only shows in the top digit, so that flip is applied to the top digit
+// by `top_xor`. What is left: integers use the key itself; negative floats are complemented
+// below the sign bit: key ^ (sign-extension of the sign bit, with the sign bit cleared).
+template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT radix_bits(KeyT k) {
+    if constexpr (IS_FLOAT) {
+        if constexpr (sizeof(KeyT) == 4) return k ^ ((KeyT)((int32_t)k >> 31) & (KeyT)0x7FFFFFFFu);
+        else return k ^ ((KeyT)((long long)k >> 63) & (KeyT)0x7FFFFFFFFFFFFFFFull);
+    } else {
+        return k;
+    }
+}
+// `top_xor` is 0x80 on the most significant digit of signed and float keys, else 0.
+template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ u32 digit_of(KeyT k, int shift, u32 top_xor) {
+    return ((u32)(radix_bits<KeyT, IS_FLOAT>(k) >> shift) & 0xFFu) ^ top_xor;
+}
+// A key whose digit is 255 at every position (pads the last, ragged tile; it ranks after every
+// real key of the tile and is never written out).
+template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT pad_key(bool signed_or_float) {
+    // integers: digits are key bytes, top digit ^0x80 when signed -> top byte 0x7F, others 0xFF.
+    // floats: a non-negative key keeps its bits -> the same pattern 0x7FFF...FF maps to all ones.
+    KeyT all = (KeyT)~(KeyT)0;
+    return signed_or_float ? (KeyT)(all >> 1) : all;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Histogram of every digit position in one read of the keys. ghist[p*256 + d] (64-bit counts).
+// ---------------------------------------------------------------------------------------------
+template <typename KeyT, bool IS_FLOAT, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+sort_histogram_kernel(const KeyT *__restrict__ keys, u64 n, u64 *ghist, int signed_or_float) {
+    constexpr int P = sizeof(KeyT);
+    constexpr int EPV = 16 / sizeof(KeyT);
+    __shared__ u32 sh[P * kRadix];
+    const u32 tid = threadIdx.x;
+    for (u32 i = tid; i < P * kRadix; i += THREADS) sh[i] = 0;
+    __syncthreads();
+
+    auto count_key = [&](KeyT k) {
+        const KeyT b = radix_bits<KeyT, IS_FLOAT>(k);
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+            u32 d = (u32)(b >> (8 * p)) & 0xFFu;
+            if (p == P - 1 && signed_or_float) d ^= 0x80u;
+            atomicAdd(&sh[p * kRadix + d], 1u);
+        }
+    };
+
+    const u64 mis = ((uintptr_t)keys & 15u) / sizeof(KeyT);
+    u64 head = mis ? (EPV - mis) : 0;
+    if (head > n) head = n;
+    const u64 nvec = (n - head) / EPV;
+    const u64 tail_start = head + nvec * EPV;
+    const uint4 *vsrc = reinterpret_cast<const uint4 *>(keys + head);
+
+    constexpr int UNROLL = 4;
+    constexpr u64 STRIP = (u64)THREADS * UNROLL;
+    const u64 stride = (u64)gridDim.x * STRIP;
+    for (u64 base = (u64)blockIdx.x * STRIP; base < nvec; base += stride) {
+        uint4 v[UNROLL];
+        bool ok[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const u64 idx = base + (u64)u * THREADS + tid;
+            ok[u] = idx < nvec;
+            if (ok[u]) v[u] = ld_stream_v4(vsrc + idx);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (ok[u]) {
+                KeyT e[EPV];
+                memcpy(e, &v[u], 16);
+#pragma unroll
+                for (int k = 0; k < EPV; ++k) count_key(e[k]);
+            }
+        }
+    }
+    if (blockIdx.x == 0) {
+        if (tid < head) count_key(keys[tid]);
+        const u64 t = tail_start + tid;
+        if (t < n) count_key(keys[t]);
+    }
+    __syncthreads();
+    for (u32 i = tid; i < P * kRadix; i += THREADS) {
+        const u32 c = sh[i];
+        if (c) atomicAdd(&ghist[i], (u64)c);
+    }
+}
+
+// Exclusive prefix over the 256 bins of each digit position, in place. One CTA of 256 threads per
+// digit position.
+__global__ void sort_scan_histogram_kernel(u64 *ghist);
+
+// ---------------------------------------------------------------------------------------------
+// One onesweep pass
+// ---------------------------------------------------------------------------------------------
+struct SortPassArgs {
+    const void *keys_in;
+    void *keys_out;
+    const void *vals_in;
+    void *vals_out;
+    u64 n;
+    u64 ntiles;
+    const u64 *gexcl;  // [256] exclusive digit offsets of this pass
+    u64 *desc;         // [ntiles][256]
+    u32 *header;
+    int pass;
+    int shift;
+    u32 top_xor;
+    int signed_or_float;
+};
+
+template <typename KeyT, typename ValT, int THREADS, int ITEMS> struct SortSmem {
+    static constexpr int WARPS = THREADS / 32;
+    static constexpr int TILE = THREADS * ITEMS;
+    static constexpr bool HAS_VAL = !std::is_same<ValT, void>::value;
+    using ValS = typename std::conditional<HAS_VAL, ValT, char>::type;  // storage type (unused without values)
+    static constexpr size_t kWhist = (size_t)WARPS * kRadix * 4;
+    static constexpr size_t kGbase = (size_t)kRadix * 8;
+    static constexpr size_t kKeys = (size_t)TILE * sizeof(KeyT);
+    static constexpr size_t kVals = HAS_VAL ? (size_t)TILE * sizeof(ValS) : 0;
+    static constexpr size_t kBytes = kWhist + kGbase + kKeys + kVals + 64;
+};
+
+template <typename KeyT, bool IS_FLOAT, typename ValT, int THREADS, int ITEMS>
+__global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512 ? 2 : 1))) onesweep_kernel(SortPassArgs a) {
+    using SM = SortSmem<KeyT, ValT, THREADS, ITEMS>;
+    using ValS = typename SM::ValS;
+    constexpr int WARPS = SM::WARPS;
+    constexpr int TILE = SM::TILE;
+    static_assert(THREADS >= kRadix && THREADS % 32 == 0, "one thread per digit is required");
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    u64 *s_gbase = reinterpret_cast<u64 *>(smem);                              // [256]
+    u32 *s_whist = reinterpret_cast<u32 *>(smem + SM::kGbase);                 // [WARPS][256]
+    KeyT *s_keys = reinterpret_cast<KeyT *>(smem + SM::kGbase + SM::kWhist);   // [TILE]
+    ValS *s_vals = reinterpret_cast<ValS *>(smem + SM::kGbase + SM::kWhist + SM::kKeys);
+    u32 *s_misc = reinterpret_cast<u32 *>(smem + SM::kGbase + SM::kWhist + SM::kKeys + SM::kVals);
+    // s_misc[0..7]: warp sums of the digit scan; [8],[9]: tile ticket; [10]: abort flag
+
+    const u32 tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
+    const KeyT *kin = static_cast<const KeyT *>(a.keys_in);
+    KeyT *kout = static_cast<KeyT *>(a.keys_out);
+
+    if (tid == 0) {
+        const u32 t = atomicAdd(&a.header[kTicketBase + 1 + a.pass], 1u);
+        s_misc[8] = t;
+        s_misc[10] = ld_relaxed_u32(&a.header[kStatusWord]) != 0u;
+    }
+    u32 *my_hist = s_whist + warp * kRadix;
+#pragma unroll
+    for (int i = 0; i < kRadix / 32; ++i) my_hist[i * 32 + lane] = 0;
+    __syncthreads();
+    const u64 tile = s_misc[8];
+    if (tile >= a.ntiles) return;
+    const u64 tag_agg = desc_tag(a.pass, kStAggregate), tag_pfx = desc_tag(a.pass, kStPrefix),
+              tag_poison = desc_tag(a.pass, kStPoison);
+    u64 *my_desc = a.desc + tile * kRadix;
+    if (s_misc[10]) {  // an earlier tile failed: pass the poison on
+        if (tid < kRadix) st_relaxed_u64(my_desc + tid, tag_poison);
+        return;
+    }
+
+    const u64 tile_start = tile * (u64)TILE;
+    const u32 count = (u32)(a.n - tile_start < (u64)TILE ? a.n - tile_start : (u64)TILE);
+    const bool full = count == (u32)TILE;
+    const u32 warp_off = warp * 32 * ITEMS + lane;  // + i*32: element offset of item i in the tile
+
+    // ---- 1. load keys (warp-striped: item i of lane l is element warp_off + 32*i) ---------------
+    KeyT key[ITEMS];
+    if (full) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) key[i] = kin[tile_start + warp_off + i * 32];
+    } else {
+        const KeyT pad = pad_key<KeyT, IS_FLOAT>(a.signed_or_float != 0);
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const u32 off = warp_off + i * 32;
+            key[i] = off < count ? kin[tile_start + off] : pad;
+        }
+    }
+
+    // ---- 2. rank each key within (warp, digit), in element order --------------------------------
+    u32 rank[ITEMS];
+    const u32 lt = lanemask_lt();
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const u32 d = digit_of<KeyT, IS_FLOAT>(key[i], a.shift, a.top_xor);
+        const u32 peers = __match_any_sync(0xFFFFFFFFu, d);
+        const int leader = __ffs(peers) - 1;
+        u32 before = 0;
+        if ((int)lane == leader) before = atomicAdd(&my_hist[d], (u32)__popc(peers));
+        before = __shfl_sync(0xFFFFFFFFu, before, leader);
+        rank[i] = before + __popc(peers & lt);
+    }
+    __syncthreads();
+
+    // ---- 3. per digit: count over the warps, publish the tile aggregate -------------------------
+    u32 cnt = 0;       // keys of digit `tid` in the tile, pads included
+    u32 cnt_real = 0;  // pads excluded (they all have digit 255)
+    if (tid < kRadix) {
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) cnt += s_whist[w * kRadix + tid];
+        cnt_real = cnt;
+        if (!full && tid == kRadix - 1) cnt_real = cnt - ((u32)TILE - count);
+        st_relaxed_u64(my_desc + tid, (tile == 0 ? tag_pfx : tag_agg) | (u64)cnt_real);
+    }
+    // ---- 4. exclusive scan of the digit counts: start of each digit's run in the sorted tile ----
+    u32 incl = cnt;
+    if (tid < kRadix) {
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const u32 up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= (u32)d) incl += up;
+        }
+        if (lane == 31) s_misc[warp] = incl;
+    }
+    __syncthreads();
+    u32 dexcl = 0;  // exclusive prefix of digit `tid` within the tile
+    if (tid < kRadix) {
+        u32 wbase = 0;
+#pragma unroll
+        for (int w = 0; w < kRadix / 32; ++w)
+            if (w < (int)warp) wbase += s_misc[w];
+        dexcl = wbase + incl - cnt;
+        // Turn the per-warp counts into the position of each (warp, digit) group in the sorted tile.
+        u32 run = dexcl;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const u32 c = s_whist[w * kRadix + tid];
+            s_whist[w * kRadix + tid] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+
+    // ---- 5. scatter keys (and values) to their sorted position in shared memory -----------------
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const u32 d = digit_of<KeyT, IS_FLOAT>(key[i], a.shift, a.top_xor);
+        rank[i] += my_hist[d];
+        s_keys[rank[i]] = key[i];
+    }
+    if constexpr (SM::HAS_VAL) {
+        const ValS *vin = static_cast<const ValS *>(a.vals_in);
+        ValS val[ITEMS];
+        if (full) {
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) val[i] = vin[tile_start + warp_off + i * 32];
+        } else {
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                const u32 off = warp_off + i * 32;
+                val[i] = off < count ? vin[tile_start + off] : (ValS)0;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) s_vals[rank[i]] = val[i];
+    }
+
+    // ---- 6. look back: keys of digit `tid` in all earlier tiles ----------------------------------
+    if (tid < kRadix) {
+        u64 excl = 0;
+        bool ok = true;
+        if (tile > 0) {
+            u64 t = tile - 1;
+            u32 spins = 0;
+            while (true) {
+                const u64 w = ld_relaxed_u64(a.desc + t * kRadix + tid);
+                const u64 tag = w & ~kCountMask;
+                if (tag == tag_pfx) {
+                    excl += w & kCountMask;
+                    break;
+                } else if (tag == tag_agg) {
+                    excl += w & kCountMask;
+                    --t;  // tile 0 always publishes a prefix, so t never passes 0
+                    spins = 0;
+                } else if (tag == tag_poison) {
+                    ok = false;
+                    break;
+                } else {
+                    if (++spins > kSpinLimit) {
+                        record_error(a.header, KF_ERR_TIMEOUT, (u32)tile);
+                        ok = false;
+                        break;
+                    }
+                    if (spins > 8) __nanosleep(spins > 64 ? 256 : 32);
+                }
+            }
+        }
+        if (ok) {
+            if (tile > 0) st_relaxed_u64(my_desc + tid, tag_pfx | (excl + (u64)cnt_real));
+            // Global index of element idx of the sorted tile with digit d: gbase[d] + idx.
+            s_gbase[tid] = a.gexcl[tid] + excl - (u64)dexcl;
+        } else {
+            st_relaxed_u64(my_desc + tid, tag_poison);
+            s_misc[10] = 1;
+        }
+    }
+    __syncthreads();
+    if (s_misc[10]) return;
+
+    // ---- 7. stream the sorted tile out: consecutive threads write consecutive addresses within
+    //         each digit's run ----------------------------------------------------------------
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const u32 idx = i * THREADS + tid;
+        if (full || idx < count) {
+            const KeyT k = s_keys[idx];
+            const u32 d = digit_of<KeyT, IS_FLOAT>(k, a.shift, a.top_xor);
+            const u64 o = s_gbase[d] + idx;
+            kout[o] = k;
+            if constexpr (SM::HAS_VAL) static_cast<ValS *>(a.vals_out)[o] = s_vals[idx];
+        }
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+struct SortVariant {
+    int threads, items;
+};
+static const SortVariant kSortVariants[] = {{256, 16}, {512, 16}, {512, 24}, {1024, 16}};
+constexpr int kNumSortVariants = 4;
+
+template <typename KeyT, bool IS_FLOAT, typename ValT, int THREADS, int ITEMS>
+int onesweep_launch_one(const SortPassArgs &a, cudaStream_t s) {
+    using SM = SortSmem<KeyT, ValT, THREADS, ITEMS>;
+    auto kern = onesweep_kernel<KeyT, IS_FLOAT, ValT, THREADS, ITEMS>;
+    if (SM::kBytes > 227 * 1024) return KF_ERR_UNSUPPORTED;
+    KF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes));
+    kern<<<(unsigned)a.ntiles, THREADS, SM::kBytes, s>>>(a);
+    KF_CUDA_TRY(cudaGetLastError());
+    return KF_OK;
+}
+
+template <typename KeyT, bool IS_FLOAT, typename ValT>
+int onesweep_launch(int variant, const SortPassArgs &a, cudaStream_t s) {
+    switch (variant) {
+    case 0: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 256, 16>(a, s);
+    case 1: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 512, 16>(a, s);
+    case 2: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 512, 24>(a, s);
+    case 3: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 1024, 16>(a, s);
+    default: return KF_ERR_UNSUPPORTED;
+    }
+}
+
+template <typename KeyT, bool IS_FLOAT>
+int histogram_launch(const void *keys, u64 n, u64 *ghist, int signed_or_float, cudaStream_t s) {
+    constexpr int THREADS = 512;
+    const int sms = device_sm_count();
+    u64 blocks = (u64)sms * 4;
+    const u64 need = (n * sizeof(KeyT) + (u64)THREADS * 64 - 1) / ((u64)THREADS * 64);
+    if (blocks > need) blocks = need < 1 ? 1 : need;
+    sort_histogram_kernel<KeyT, IS_FLOAT, THREADS><<<(unsigned)blocks, THREADS, 0, s>>>(
+        static_cast<const KeyT *>(keys), n, ghist, signed_or_float);
+    KF_CUDA_TRY(cudaGetLastError());
+    return KF_OK;
+}
+
+// Per key width, defined in sort_inst_*.cu. val_bytes in {0, 4, 8}.
+int sort_pass_k32(bool is_float, int val_bytes, int variant, const SortPassArgs &a, cudaStream_t s);
+int sort_pass_k64(bool is_float, int val_bytes, int variant, const SortPassArgs &a, cudaStream_t s);
+int sort_hist_k32(bool is_float, const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s);
+int sort_hist_k64(bool is_float, const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s);
+
+#define KF_SORT_INSTANTIATE(NAME, KeyT)                                                               \
+    namespace kf {                                                                                    \
+    int sort_pass_##NAME(bool is_float, int val_bytes, int variant, const SortPassArgs &a,            \
+                         cudaStream_t s) {                                                            \
+        if (is_float) {                                                                               \
+            if (val_bytes == 0) return onesweep_launch<KeyT, true, void>(variant, a, s);              \
+            if (val_bytes == 4) return onesweep_launch<KeyT, true, uint32_t>(variant, a, s);          \
+            if (val_bytes == 8) return onesweep_launch<KeyT, true, u64>(variant, a, s);               \
+        } else {                                                                                      \
+            if (val_bytes == 0) return onesweep_launch<KeyT, false, void>(variant, a, s);             \
+            if (val_bytes == 4) return onesweep_launch<KeyT, false, uint32_t>(variant, a, s);         \
+            if (val_bytes == 8) return onesweep_launch<KeyT, false, u64>(variant, a, s);              \
+        }                                                                                             \
+        return KF_ERR_UNSUPPORTED;                                                                    \
+    }                                                                                                 \
+    int sort_hist_##NAME(bool is_float, const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s) { \
+        return is_float ? histogram_launch<KeyT, true>(keys, n, ghist, sof, s)                        \
+                        : histogram_launch<KeyT, false>(keys, n, ghist, sof, s);                      \
+    }                                                                                                 \
+    }
+
+}  // namespace kf

@@ -1,0 +1,235 @@
+"""Sharded (multi-GPU) mapreduce, scan and sample sort: one process per GPU over torch.distributed.
+
+The reference has no multi-device layer; this one follows the plan the primitives suggest. Every
+rank owns one contiguous shard of a global array (rank order = array order) and each primitive is
+"local kernel(s) + ONE small exchange":
+
+  mapreduce : local mapreduce -> allreduce of one partial per rank (allgather + ordered fold for
+              the operators NCCL cannot reduce) -> g.
+  scan      : local reduce -> allgather of the shard totals -> exclusive fold of the totals in
+              rank order -> local scan seeded with the carry (12n bytes instead of the 16n of
+              "scan, then fix up"). Non-commutative operators (AffineCompose) take the ordered
+              route: local scan for the total, then the seeded scan.
+  sort      : local onesweep sort -> 1024 regular samples per rank, allgather, identical splitter
+              choice everywhere -> cut the sorted shard at the splitters (kf_upper_bounds) ->
+              all-to-all of the runs (NCCL, over NVLink) -> local onesweep sort of the received
+              runs (keys only, so re-sorting is bit-exact and stable order is irrelevant).
+
+Remote data always lands in local HBM through NCCL before a kernel touches it. The local steps go
+through `LocalOps`, whose default implementation calls the CUDA kernels; the CPU tests of the
+exchange logic inject a host implementation instead (gloo backend).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _cabi as C
+from . import ops
+from .allocations import Scan1D, get_allocation
+from .mapreduce import mapreduce_
+from .scan import scan_ as _scan_
+from .sort import sort_ as _sort_
+
+SAMPLES_PER_RANK = 1024
+
+
+class ShardGroup:
+    """The ranks that share one sharded array (a torch.distributed process group)."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+
+
+class LocalOps:
+    """Local (per-shard) steps on the GPU through libkf_b200.so."""
+
+    def reduce(self, f, op, x):
+        out = torch.empty(1, dtype=x.dtype, device=x.device)
+        return mapreduce_(f, op, out, x)
+
+    def fold(self, op, partials, g=ops.identity):
+        """op-reduction of a handful of partials (one per rank), then g."""
+        out = torch.empty(1, dtype=partials.dtype, device=partials.device)
+        return mapreduce_(ops.identity, op, out, partials, g=g)
+
+    def scan_(self, f, op, dst, src, init=None, tmp=None):
+        return _scan_(f, op, dst, src, init=init, tmp=tmp)
+
+    def sort(self, x):
+        return _sort_(torch.empty_like(x), x)
+
+    def upper_bounds(self, sorted_keys, splitters):
+        out = torch.empty(splitters.numel(), dtype=torch.int64, device=sorted_keys.device)
+        with torch.cuda.device(sorted_keys.device):
+            rc = C.load().kf_upper_bounds(ops.dtype_code(sorted_keys), sorted_keys.data_ptr(), sorted_keys.numel(),
+                                          splitters.data_ptr(), splitters.numel(), out.data_ptr(),
+                                          ops.stream_handle(sorted_keys))
+        C.check(rc, "upper_bounds")
+        return out
+
+    def take(self, x, positions):
+        """x[positions] for a small index tensor (sample extraction)."""
+        return x[positions]
+
+
+_DEFAULT_OPS = LocalOps()
+_NCCL_REDUCE = {C.OP_ADD: dist.ReduceOp.SUM, C.OP_MUL: dist.ReduceOp.PRODUCT, C.OP_MIN: dist.ReduceOp.MIN,
+                C.OP_MAX: dist.ReduceOp.MAX}
+_NCCL_DTYPES = {torch.float32, torch.float64, torch.int32, torch.int64, torch.uint8, torch.int8}
+
+
+def _bits_view(t):
+    """Collectives move opaque bits: unsigned 16/32/64-bit tensors travel as their signed twins."""
+    twin = {getattr(torch, "uint16", None): torch.int16, getattr(torch, "uint32", None): torch.int32,
+            getattr(torch, "uint64", None): torch.int64}
+    return t.view(twin[t.dtype]) if t.dtype in twin else t
+
+
+def all_gather_vec(group: ShardGroup, x):
+    """Concatenation over ranks of equally sized 1-D tensors."""
+    out = torch.empty(group.world * x.numel(), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(_bits_view(out), _bits_view(x.contiguous()), group=group.group)
+    return out
+
+
+# ---- mapreduce -----------------------------------------------------------------------------------
+def mapreduce(group: ShardGroup, f, op, x, *, g=ops.identity, local: LocalOps = _DEFAULT_OPS, to_cpu=True):
+    """Global g(op-reduce f(x)) over all shards; every rank gets the value."""
+    opcode = ops.op_code(op)
+    if opcode == C.OP_AFFINE:
+        raise C.ArgumentError("AffineCompose is not commutative: use scan")
+    part = local.reduce(f, op, x)
+    if opcode in _NCCL_REDUCE and part.dtype in _NCCL_DTYPES:
+        dist.all_reduce(part, op=_NCCL_REDUCE[opcode], group=group.group)
+        total = local.fold(op, part, g=g)  # one element: applies g
+    else:
+        total = local.fold(op, all_gather_vec(group, part), g=g)
+    return total.cpu()[0].item() if to_cpu else total
+
+
+# ---- scan ----------------------------------------------------------------------------------------
+def scan_(group: ShardGroup, *args, tmp=None, local: LocalOps = _DEFAULT_OPS):
+    """Sharded `scan!([f,] op, dst, src)`: dst holds this rank's shard of the global inclusive scan."""
+    if len(args) == 3:
+        f, (op, dst, src) = ops.identity, args
+    else:
+        f, op, dst, src = args
+    affine = isinstance(op, ops.AffineCompose)
+    if affine:
+        # ordered route: the shard total is the last element of a local scan
+        local.scan_(f, op, dst, src, tmp=tmp)
+        if isinstance(dst, (tuple, list)):
+            total = torch.stack([dst[0][-1], dst[1][-1]])
+        else:
+            total = dst[-1].clone()
+        totals = all_gather_vec(group, total).view(group.world, 2)
+        if group.rank == 0:
+            return dst
+        carry = local.scan_(f, op, torch.empty_like(totals), totals)[group.rank - 1].contiguous()
+        return local.scan_(f, op, dst, src, init=carry, tmp=tmp)
+    total = local.reduce(f, op, src)
+    totals = all_gather_vec(group, total)
+    init = None
+    if group.rank > 0:
+        # inclusive scan of the G totals; the carry into shard r is entry r-1
+        init = local.scan_(ops.identity, op, torch.empty_like(totals), totals)[group.rank - 1: group.rank]
+    return local.scan_(f, op, dst, src, init=init, tmp=tmp)
+
+
+# ---- sample sort ---------------------------------------------------------------------------------
+def choose_splitters(sorted_samples, world: int):
+    """world-1 splitters from the globally sorted samples: every world-th quantile."""
+    per = sorted_samples.numel() // world
+    pos = torch.arange(1, world, device=sorted_samples.device) * per
+    return sorted_samples[pos]
+
+
+def sort(group: ShardGroup, x, *, local: LocalOps = _DEFAULT_OPS, samples_per_rank: int = SAMPLES_PER_RANK):
+    """Sample sort of the sharded keys `x`. Returns (sorted_chunk, counts): rank r holds the r-th
+    contiguous piece of the globally sorted array; `counts` (host list) are the piece lengths."""
+    world, rank = group.world, group.rank
+    n = x.numel()
+    mine = local.sort(x)
+    if world == 1:
+        return mine, [n]
+    # 1. regular samples of the sorted shard
+    s = samples_per_rank
+    pos = ((torch.arange(s, device=x.device, dtype=torch.float64) + 0.5) * (n / s)).to(torch.int64).clamp_(0, max(n - 1, 0))
+    samples = local.take(mine, pos) if n > 0 else torch.zeros(s, dtype=x.dtype, device=x.device)
+    all_samples = local.sort(all_gather_vec(group, samples))
+    splitters = choose_splitters(all_samples, world)
+    # 2. cut the sorted shard: run j goes to rank j
+    cuts = local.upper_bounds(mine, splitters)
+    bounds = torch.cat([torch.zeros(1, dtype=torch.int64, device=x.device), cuts,
+                        torch.full((1,), n, dtype=torch.int64, device=x.device)])
+    send_counts = bounds[1:] - bounds[:-1]
+    count_matrix = all_gather_vec(group, send_counts).view(world, world).cpu()
+    send = [int(v) for v in count_matrix[rank]]
+    recv = [int(v) for v in count_matrix[:, rank]]
+    # 3. all-to-all of the runs
+    inbox = torch.empty(sum(recv), dtype=x.dtype, device=x.device)
+    dist.all_to_all_single(_bits_view(inbox), _bits_view(mine), output_split_sizes=recv, input_split_sizes=send,
+                           group=group.group)
+    # 4. merge = one more local sort of the received sorted runs
+    out = local.sort(inbox) if inbox.numel() else inbox
+    counts = [int(v) for v in count_matrix.sum(dim=0)]
+    return out, counts
+
+
+# ---- host-buffer pipeline (end-to-end path) --------------------------------------------------------
+class HostScanPipeline:
+    """`scan!` for arrays that live in pinned HOST memory.
+
+    The input is cut into chunks; chunk c is copied in on one stream, scanned on a second stream
+    with `init` = the last output element of chunk c-1 (still on the device), and copied out on a
+    third, so the two PCIe directions and the kernel overlap. Device staging buffers and the scan
+    workspace are allocated once.
+    """
+
+    def __init__(self, kf_module, max_n: int, chunks: int = 8, device=None):
+        self.kf = kf_module
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.max_n = max_n
+        self.chunks = chunks
+        self.stage_in = torch.empty(max_n * 8, dtype=torch.uint8, device=self.device)
+        self.stage_out = torch.empty(max_n * 8, dtype=torch.uint8, device=self.device)
+        self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+        self._tmp = {}
+
+    def scan_host(self, op, dst_host, src_host, f=ops.identity):
+        n = src_host.numel()
+        if n > self.max_n or src_host.element_size() > 8:
+            raise C.ArgumentError("HostScanPipeline was sized for %d elements of at most 8 bytes" % self.max_n)
+        if dst_host.numel() != n or dst_host.dtype != src_host.dtype:
+            raise C.ArgumentError("dst and src must match in length and element type")
+        dt = src_host.dtype
+        es = src_host.element_size()
+        d_in = self.stage_in[: n * es].view(dt)
+        d_out = self.stage_out[: n * es].view(dt)
+        per = -(-n // self.chunks)
+        key = (dt, per)
+        if key not in self._tmp:
+            self._tmp[key] = get_allocation(Scan1D, f, op, d_in[:per])
+        tmp = self._tmp[key]
+        cur = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        self.s_cmp.wait_stream(cur)
+        lo = 0
+        while lo < n:
+            hi = min(n, lo + per)
+            with torch.cuda.stream(self.s_in):
+                d_in[lo:hi].copy_(src_host[lo:hi], non_blocking=True)
+            self.s_cmp.wait_stream(self.s_in)
+            with torch.cuda.stream(self.s_cmp):
+                init = d_out[lo - 1: lo] if lo > 0 else None
+                _scan_(f, op, d_out[lo:hi], d_in[lo:hi], init=init, tmp=tmp)
+            self.s_out.wait_stream(self.s_cmp)
+            with torch.cuda.stream(self.s_out):
+                dst_host[lo:hi].copy_(d_out[lo:hi], non_blocking=True)
+            lo = hi
+        cur.wait_stream(self.s_out)
+        return dst_host

@@ -1,0 +1,150 @@
+"""GPU parity tests of `mapreduce` against the CPU oracle, through the C ABI.
+
+Mirrors test/tests/mapreduce/mapreduce1d_test.jl:7-56,218-224 and the dims=nothing cases of
+test/tests/mapreduce/mapreduce_test.jl of KernelForge.jl. Tolerances: integers bit-exact; floats
+rtol 1e-4 / atol 1e-5 on the reference's sum(1:n) cases, and 1e-5*log2(n) relative against the
+Float64 oracle elsewhere.
+"""
+import math
+import operator
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from util import scan_tol, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+NP_OPS = {"+": 0, "*": 1, "min": 2, "max": 3, "&": 4, "|": 5, "xor": 6}
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.int32])
+@pytest.mark.parametrize("n", [100_000, 10_001, 100, 33])
+def test_sum_1_to_n(kf, dtype, n):
+    """sum(1:n), allocating and in-place forms, fresh and reused tmp (flag reset between calls)."""
+    src_h = np.arange(1, n + 1).astype(dtype)
+    src = to_dev(src_h)
+    ref = n * (n + 1) // 2
+    if dtype == np.int32:
+        ref = int(np.array([ref]).astype(np.int64).astype(np.int32)[0])  # Int32 `+` wraps
+    tmp = kf.get_allocation(kf.MapReduce1D, kf.identity, operator.add, src)
+    for trial in range(3):
+        dst = torch.zeros(1, dtype=src.dtype, device="cuda")
+        kf.mapreduce1d_(kf.identity, operator.add, dst, src, tmp=tmp)
+        got_inplace = dst.cpu()[0].item()
+        got = kf.mapreduce1d(kf.identity, operator.add, src, to_cpu=True)
+        got_tmp = kf.mapreduce(kf.identity, operator.add, src, tmp=tmp)
+        for g in (got_inplace, got, got_tmp):
+            if dtype == np.int32:
+                assert g == ref
+            else:
+                assert math.isclose(g, ref, rel_tol=1e-4, abs_tol=1e-5)
+
+
+def test_config_abs2_sum_2p20(kf, oracle):
+    """mapreduce(abs2, +, x), Float32 n=2^20, x ~ U[0,1) seed 0; 1e-5*log2(n) relative vs Float64."""
+    n = 1 << 20
+    x = np.random.default_rng(0).random(n, dtype=np.float32)
+    ref = oracle.c_mapreduce(oracle.MAP_ABS2, oracle.OP_ADD, x)
+    got = kf.mapreduce(kf.abs2, operator.add, to_dev(x))
+    assert abs(got - ref) <= scan_tol(n) * abs(ref)
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8, np.int16, np.int32, np.uint32, np.int64, np.uint64])
+@pytest.mark.parametrize("op", ["+", "*", "min", "max", "&", "|", "xor"])
+def test_integer_ops_exact(kf, oracle, dtype, op):
+    rng = np.random.default_rng(zlib.crc32((np.dtype(dtype).name + op).encode()))
+    info = np.iinfo(dtype)
+    for n in (1, 31, 1000, 100_003):
+        x = rng.integers(info.min, info.max, size=n, dtype=dtype, endpoint=True)
+        if op == "*":
+            x = (x | 1).astype(dtype)  # odd factors keep the wrapped product away from 0
+        ref = oracle.c_mapreduce(oracle.MAP_IDENTITY, NP_OPS[op], x)
+        got = kf.mapreduce(kf.identity, op, to_dev(x))
+        assert int(got) == int(ref), (n, got, ref)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("f,op", [("identity", "+"), ("abs2", "+"), ("abs", "max"), ("identity", "min"),
+                                  ("identity", "max"), ("identity", "*")])
+def test_float_ops(kf, oracle, dtype, f, op):
+    rng = np.random.default_rng(7)
+    fcode = {"identity": 0, "abs2": 1, "abs": 2}[f]
+    for n in (1, 5, 1000, 300_001):
+        x = rng.standard_normal(n).astype(dtype)
+        if op == "*":
+            x = (1.0 + 1e-3 * x / max(1.0, math.sqrt(n))).astype(dtype)
+        ref = oracle.c_mapreduce(fcode, NP_OPS[op], x)
+        got = kf.mapreduce(f, op, to_dev(x))
+        if op in ("min", "max"):
+            assert got == ref
+        else:
+            scale = float(np.abs(x.astype(np.float64)).sum()) if op == "+" and f == "identity" else abs(ref)
+            assert abs(got - ref) <= scan_tol(n) * max(scale, 1e-30)
+
+
+def test_post_map_sqrt(kf, oracle):
+    x = np.random.default_rng(3).random(12345, dtype=np.float32)
+    ref = math.sqrt(oracle.c_mapreduce(oracle.MAP_ABS2, oracle.OP_ADD, x))
+    got = kf.mapreduce(kf.abs2, operator.add, to_dev(x), g=math.sqrt)
+    assert abs(got - ref) <= 1e-5 * 14 * ref
+
+
+@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (256, 8)])
+@pytest.mark.parametrize("blocks", [None, 1, 7, 148, 1184])
+def test_launch_overrides(kf, workgroup, nitem, blocks):
+    n = 1_000_003
+    x = np.random.default_rng(1).integers(0, 1 << 32, size=n, dtype=np.uint32)
+    ref = int(x.sum(dtype=np.uint64) & 0xFFFFFFFF)
+    got = kf.mapreduce(kf.identity, "+", to_dev(x), workgroup=workgroup, Nitem=nitem, blocks=blocks)
+    assert int(got) == ref
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.identity, "+", to_dev(x), workgroup=96, Nitem=3)
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.uint8, np.int32])
+@pytest.mark.parametrize("offset", [1, 2, 3, 5])
+def test_views_unaligned(kf, oracle, dtype, offset):
+    """view(x, 2:n)-style base pointers (test/tests/views/views_test.jl:14-23)."""
+    n = 70_001
+    x = (np.random.default_rng(offset).integers(0, 100, size=n)).astype(dtype)
+    ref = oracle.c_mapreduce(0, 0, x)
+    got = kf.mapreduce(kf.identity, "+", to_dev(x, offset=offset))
+    assert got == ref
+
+
+def test_errors(kf):
+    x = torch.ones(100, dtype=torch.float32, device="cuda")
+    small = kf.KernelBuffer(kf.MapReduce1D, torch.empty(16, dtype=torch.uint8, device="cuda"))
+    with pytest.raises(kf.KernelForgeError):  # wrong-size tmp must throw
+        kf.mapreduce(kf.identity, "+", x, tmp=small)
+    with pytest.raises(kf.ArgumentError):  # empty reduction
+        kf.mapreduce(kf.identity, "+", x[:0])
+    with pytest.raises(kf.ArgumentError):  # unsupported closure: no fallback
+        kf.mapreduce(lambda v: v + 1, "+", x)
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.identity, lambda a, b: a - b, x)
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.identity, "+", x, dims=1)
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.identity, "+", x.cpu())
+    assert kf.mapreduce(kf.identity, "+", x) == 100.0  # the context survives the rejected calls
+
+
+def test_full_size_2p28(kf):
+    """n = 2^28: UInt32 wrapping sum bit-exact and Float32 sum within tolerance, checked against
+    torch reductions in wider types on the same device data."""
+    n = 1 << 28
+    g = torch.Generator(device="cuda").manual_seed(0)
+    xi = torch.randint(0, 256, (n,), dtype=torch.int32, device="cuda", generator=g)
+    ref = int(xi.sum(dtype=torch.int64).item()) & 0xFFFFFFFF
+    got = kf.mapreduce(kf.identity, "+", xi.view(torch.uint32))
+    assert int(got) == ref
+    xf = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+    reff = xf.sum(dtype=torch.float64).item()
+    gotf = kf.mapreduce(kf.identity, "+", xf)
+    assert abs(gotf - reff) <= scan_tol(n) * reff
+    # determinism: same input, same launch -> same bits
+    assert kf.mapreduce(kf.identity, "+", xf) == gotf

@@ -1,0 +1,257 @@
+"""GPU parity tests of `scan` / `scan!` against the CPU oracle, through the C ABI.
+
+Mirrors test/tests/scan/scan_test.jl of KernelForge.jl (sizes and types :35-65, UInt8 wrap :67-86,
+n=1..10 :88-102, reused tmp :107-125, non-commutative operator :22-33) and the unaligned views of
+test/tests/views/views_test.jl. Tolerances: integers bit-exact; floats 1e-5*log2(n) relative to
+the Float64 left fold (for `+`, relative to the running sum of |x|, which equals the fold for
+non-negative data).
+"""
+import numpy as np
+import pytest
+import torch
+
+from util import assert_close_rel, scan_tol, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+OPC = {"+": 0, "*": 1, "min": 2, "max": 3, "&": 4, "|": 5, "xor": 6}
+
+
+def _check_scan(kf, oracle, x, op, **kw):
+    ref = oracle.c_scan(0, OPC[op], x)
+    dst = kf.scan(op, to_dev(x), **kw)
+    got = to_host(dst)
+    if x.dtype.kind == "f":
+        if op == "+":
+            floor = np.cumsum(np.abs(x.astype(np.float64)))
+            err = np.abs(got.astype(np.float64) - ref)
+            assert (err <= scan_tol(x.size) * np.maximum(floor, 1e-300)).all(), float((err / floor).max())
+        elif op in ("min", "max"):
+            assert (got.astype(np.float64) == ref).all()
+        else:
+            assert_close_rel(got, ref, x.size)
+    else:
+        assert (got == ref).all()
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.int32])
+@pytest.mark.parametrize("op", ["+", "min"])
+@pytest.mark.parametrize("n", [1, 5, 10, 100, 1000, 1_000_000])
+def test_sizes_types_ops(kf, oracle, dtype, op, n):
+    rng = np.random.default_rng(n)
+    x = rng.random(n).astype(dtype) if dtype == np.float64 else rng.integers(-1000, 1000, n).astype(dtype)
+    _check_scan(kf, oracle, x, op)
+
+
+@pytest.mark.parametrize("n", list(range(1, 11)))
+def test_edge_sizes_f64(kf, oracle, n):
+    _check_scan(kf, oracle, np.random.default_rng(n).random(n), "+")
+
+
+@pytest.mark.parametrize("op", ["+", "max", "min"])
+def test_uint8_wrapping(kf, oracle, op):
+    for trial in range(5):
+        x = np.random.default_rng(trial).integers(0, 256, 10_001).astype(np.uint8)
+        _check_scan(kf, oracle, x, op)
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8, np.int16, np.uint32, np.int64, np.uint64, np.float32])
+@pytest.mark.parametrize("op", ["+", "*", "max", "&", "|", "xor"])
+def test_dtype_op_matrix(kf, oracle, dtype, op):
+    if np.dtype(dtype).kind == "f" and op in ("&", "|", "xor"):
+        with pytest.raises(kf.ArgumentError):
+            kf.scan(op, torch.ones(8, dtype=torch.float32, device="cuda"))
+        return
+    rng = np.random.default_rng(11)
+    n = 70_003
+    if np.dtype(dtype).kind == "f":
+        x = (1.0 + 1e-4 * rng.standard_normal(n)).astype(dtype) if op == "*" else rng.random(n).astype(dtype)
+    else:
+        info = np.iinfo(dtype)
+        x = rng.integers(info.min, info.max, size=n, dtype=dtype, endpoint=True)
+    _check_scan(kf, oracle, x, op)
+
+
+def test_float32_mul_long(kf, oracle):
+    n = 1_000_000
+    x = np.exp(np.random.default_rng(5).standard_normal(n) * 1e-3).astype(np.float32)
+    _check_scan(kf, oracle, x, "*")
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float32, np.float64])
+@pytest.mark.parametrize("n", [1000, 100_000, 1_000_000])
+def test_reused_tmp(kf, oracle, dtype, n):
+    """Same tmp, different data each call: a stale descriptor would leak into the next call."""
+    src = torch.zeros(n, dtype=getattr(torch, np.dtype(dtype).name), device="cuda")
+    dst = torch.zeros_like(src)
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", src)
+    for call in range(6):
+        h = np.random.default_rng(call).integers(-4, 5, n).astype(dtype)
+        src.copy_(torch.from_numpy(h))
+        kf.scan_("+", dst, src, tmp=tmp)
+        assert (to_host(dst) == np.cumsum(h, dtype=dtype)).all()  # small integers: exact in every type
+
+
+@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (512, 2), (1024, 2)])
+def test_launch_variants(kf, oracle, workgroup, nitem):
+    x = np.random.default_rng(2).integers(0, 256, 3_000_017).astype(np.uint32)
+    _check_scan(kf, oracle, x, "+", workgroup=workgroup, Nitem=nitem)
+    with pytest.raises(kf.ArgumentError):
+        kf.scan("+", to_dev(x), workgroup=96, Nitem=3)
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.uint8, np.uint32])
+@pytest.mark.parametrize("off_src,off_dst", [(1, 1), (3, 3), (1, 2), (0, 3), (5, 0)])
+def test_views_unaligned(kf, oracle, dtype, off_src, off_dst):
+    n = 40_003
+    x = np.random.default_rng(off_src * 7 + off_dst).integers(0, 200, n).astype(dtype)
+    src = to_dev(x, offset=off_src)
+    dst = to_dev(np.zeros(n, dtype=dtype), offset=off_dst)
+    kf.scan_("+", dst, src)
+    ref = oracle.c_scan(0, 0, x)
+    assert (to_host(dst).astype(np.float64) == ref.astype(np.float64)).all()
+
+
+def test_in_place_and_init(kf, oracle):
+    n = 500_001
+    x = np.random.default_rng(9).integers(0, 1 << 32, n, dtype=np.uint32)
+    t = to_dev(x)
+    kf.scan_("+", t, t)
+    assert (to_host(t) == np.cumsum(x, dtype=np.uint32)).all()
+    init = to_dev(np.array([12345], dtype=np.uint32))
+    got = to_host(kf.scan("+", to_dev(x), init=init))
+    assert (got == (np.cumsum(x, dtype=np.uint32) + np.uint32(12345))).all()
+    assert kf.scan("+", to_dev(x)[:0]).numel() == 0  # n == 0 is a no-op
+
+
+def test_map_before_scan(kf, oracle):
+    x = np.random.default_rng(4).integers(-50, 50, 30_001).astype(np.int32)
+    got = to_host(kf.scan(kf.abs2, "+", to_dev(x)))
+    assert (got == oracle.c_scan(oracle.MAP_ABS2, 0, x)).all()
+    got = to_host(kf.scan(abs, "max", to_dev(x)))
+    assert (got == oracle.c_scan(oracle.MAP_ABS, 3, x)).all()
+
+
+def _affine_inputs(n, seed):
+    rng = np.random.default_rng(seed)
+    a = (0.5 + 0.5 * rng.random(n)).astype(np.float32)
+    b = (2.0 * rng.random(n) - 1.0).astype(np.float32)
+    return a, b
+
+
+def _check_affine(n, ga, gb, ra, rb):
+    """|got - ref| <= tol * max(|ref|, s): s = 1 for the offsets b (a stationary process that
+    crosses zero), s = 4*FLT_MIN for the gains a (which decay through the subnormals to 0)."""
+    assert_close_rel(gb, rb, n, floor=1.0)
+    assert_close_rel(ga, ra, n, floor=4 * float(np.finfo(np.float32).tiny))
+
+
+@pytest.mark.parametrize("n", [1, 2, 5, 1000, 100_003, 2_000_000])
+def test_affine_soa_and_aos(kf, oracle, n):
+    """Non-commutative operator: composition of affine maps, both layouts, vs the Float64 left fold."""
+    a, b = _affine_inputs(n, n)
+    ra, rb = oracle.c_scan_affine(a, b)
+    op = kf.AffineCompose()
+    da, db = kf.scan(op, (to_dev(a), to_dev(b)))
+    _check_affine(n, to_host(da), to_host(db), ra, rb)
+    ab = np.stack([a, b], axis=1).copy()
+    out = to_host(kf.scan(op, to_dev(ab.reshape(-1)).view(n, 2)))
+    _check_affine(n, out[:, 0], out[:, 1], ra, rb)
+
+
+def test_affine_order_matters(kf, oracle):
+    """Exact small-integer maps: any swap of operands would change the result."""
+    n = 4099
+    rng = np.random.default_rng(1)
+    a = rng.integers(1, 3, n).astype(np.float32)
+    a[10:] = 1.0  # gains <= 2^10 and offsets below 2^24: every intermediate is an exact Float32 integer
+    b = rng.integers(-3, 4, n).astype(np.float32)
+    ra, rb = oracle.c_scan_affine(a, b)
+    da, db = kf.scan(kf.AffineCompose(), (to_dev(a), to_dev(b)))
+    assert (to_host(da).astype(np.float64) == ra).all()
+    assert (to_host(db).astype(np.float64) == rb).all()
+
+
+def test_affine_init_and_views(kf, oracle):
+    n = 50_001
+    a, b = _affine_inputs(n, 3)
+    init = np.array([0.75, -0.5], dtype=np.float32)
+    ra, rb = oracle.c_scan_affine(a, b, init=init.astype(np.float64))
+    da, db = kf.scan(kf.AffineCompose(), (to_dev(a, offset=1), to_dev(b, offset=1)), init=to_dev(init))
+    _check_affine(n, to_host(da), to_host(db), ra, rb)
+    # different misalignment of the four arrays -> element-wise path
+    oa = to_dev(np.zeros(n, np.float32), offset=2)
+    ob = to_dev(np.zeros(n, np.float32), offset=3)
+    kf.scan_(kf.AffineCompose(), (oa, ob), (to_dev(a), to_dev(b, offset=1)))
+    ra, rb = oracle.c_scan_affine(a, b)
+    _check_affine(n, to_host(oa), to_host(ob), ra, rb)
+
+
+def test_errors(kf):
+    x = torch.ones(100, dtype=torch.float32, device="cuda")
+    with pytest.raises(kf.ArgumentError):
+        kf.scan(lambda a, b: a - b, x)
+    with pytest.raises(kf.ArgumentError):
+        kf.scan("+", x, g=lambda v: v * 2)
+    with pytest.raises(kf.ArgumentError):
+        kf.scan_("+", torch.empty(99, dtype=torch.float32, device="cuda"), x)
+    small = kf.KernelBuffer(kf.Scan1D, torch.empty(64, dtype=torch.uint8, device="cuda"))
+    with pytest.raises(kf.KernelForgeError):
+        kf.scan("+", x, tmp=small)
+    assert kf.lib.kf_check(kf.get_allocation(kf.Scan1D, kf.identity, "+", x).ptr(), None) >= 0
+
+
+def test_full_size_2p28_uint32(kf):
+    """n = 2^28, UInt32 ~ U{0..255}, wrapping add, bit-exact: verified by the size-independent
+    property dst[0] == x[0], dst[i] - dst[i-1] == x[i] (wrapping) on the device, plus the total."""
+    n = 1 << 28
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randint(0, 256, (n,), dtype=torch.int32, device="cuda", generator=g)
+    dst = torch.empty_like(x)
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", x.view(torch.uint32))
+    kf.scan_("+", dst.view(torch.uint32), x.view(torch.uint32), tmp=tmp)
+    assert kf.lib.kf_check(tmp.ptr(), None) == 0
+    assert bool((dst[0] == x[0]).item())
+    assert bool(((dst[1:] - dst[:-1]) == x[1:]).all().item())  # int32 subtraction wraps like uint32
+    total = int(x.sum(dtype=torch.int64).item()) & 0xFFFFFFFF
+    assert (int(dst[-1].item()) & 0xFFFFFFFF) == total
+    assert total != int(x.sum(dtype=torch.int64).item())  # the running sum really wrapped
+
+
+def test_full_size_2p28_float32(kf):
+    """n = 2^28, Float32 ~ U[0,1): element-wise within 1e-5*log2(n) = 2.8e-4 relative of a Float64
+    cumulative sum of the same device data."""
+    n = 1 << 28
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+    dst = kf.scan("+", x)
+    ref = torch.cumsum(x.double(), 0)
+    rel = ((dst.double() - ref).abs() / ref.clamp_min(1e-30)).max().item()
+    assert rel <= scan_tol(n), rel
+
+
+def test_full_size_2p26_affine(kf):
+    """n = 2^26 affine maps, two Float32 arrays: compared on the device with a Float64 blocked
+    evaluation of the same left fold (exact composition per block of 2^16, then a sequential carry
+    over the 1024 block summaries)."""
+    n = 1 << 26
+    g = torch.Generator(device="cuda").manual_seed(2)
+    a = 0.5 + 0.5 * torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+    b = 2.0 * torch.rand(n, dtype=torch.float32, device="cuda", generator=g) - 1.0
+    da, db = kf.scan(kf.AffineCompose(), (a, b))
+    # B_i = a_i*B_{i-1} + b_i forgets its past geometrically (a <= 1, E[log2 a] ~ -0.44): a window of
+    # 4096 predecessors reproduces it far below the tolerance. Check random windows in Float64.
+    idx = torch.randint(4096, n, (64,), generator=torch.Generator().manual_seed(3)).tolist() + [n - 1, 4096]
+    tol = scan_tol(n)
+    for i in idx:
+        aw = a[i - 4095:i + 1].double().cpu().numpy()
+        bw = b[i - 4095:i + 1].double().cpu().numpy()
+        B = 0.0
+        for k in range(4096):
+            B = aw[k] * B + bw[k]
+        assert abs(db[i].item() - B) <= tol * max(abs(B), 1.0)
+    assert bool((da[2000:] == 0).all().item())  # the running gain has underflowed to exactly 0
+    a_h = a[:2000].double().cpu().numpy()
+    refA = np.cumprod(a_h)
+    got = da[:2000].double().cpu().numpy()
+    assert (np.abs(got - refA) <= tol * np.maximum(refA, 4 * float(np.finfo(np.float32).tiny))).all()
