@@ -101,7 +101,8 @@ int32_t kf_abi_version(void);
  * (e.g. src/sort/sort1d.jl:348-349,367-389). */
 const char *kf_error_string(int32_t status);
 
-/* The CUDA runtime error code behind the calling thread's last KF_ERR_LAUNCH_FAILED (0 if none). */
+/* The CUDA runtime error code behind the calling thread's last KF_ERR_LAUNCH_FAILED (0 if none).
+ * No counterpart in the reference (CUDA.jl raises its own exceptions). */
 int32_t kf_last_cuda_error(void);
 
 /* Reads the device-side status word of a workspace after synchronising `stream`.

@@ -122,6 +122,7 @@ template <> struct IsFloat<float> { static constexpr bool value = true; };
 template <> struct IsFloat<double> { static constexpr bool value = true; };
 
 struct OpAdd {
+    static constexpr bool commutative = true;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l + r); }
     // -0.0 is the exact additive identity of IEEE floats (+0.0 would turn a leading -0.0 into +0.0).
     template <typename T> static __device__ __forceinline__ T identity() {
@@ -130,26 +131,32 @@ struct OpAdd {
     }
 };
 struct OpMul {
+    static constexpr bool commutative = true;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l * r); }
     template <typename T> static __device__ __forceinline__ T identity() { return (T)1; }
 };
 struct OpMin {
+    static constexpr bool commutative = true;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return r < l ? r : l; }
     template <typename T> static __device__ __forceinline__ T identity() { return Limits<T>::hi(); }
 };
 struct OpMax {
+    static constexpr bool commutative = true;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return l < r ? r : l; }
     template <typename T> static __device__ __forceinline__ T identity() { return Limits<T>::lo(); }
 };
 struct OpAnd {
+    static constexpr bool commutative = true;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l & r); }
     template <typename T> static __device__ __forceinline__ T identity() { return (T)~(T)0; }
 };
 struct OpOr {
+    static constexpr bool commutative = true;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l | r); }
     template <typename T> static __device__ __forceinline__ T identity() { return (T)0; }
 };
 struct OpXor {
+    static constexpr bool commutative = true;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) { return (T)(l ^ r); }
     template <typename T> static __device__ __forceinline__ T identity() { return (T)0; }
 };
@@ -161,6 +168,7 @@ struct Affine {
     float a, b;
 };
 struct OpAffine {
+    static constexpr bool commutative = false;
     template <typename T> static __device__ __forceinline__ T apply(T l, T r) {
         T o;
         o.a = l.a * r.a;
@@ -231,6 +239,23 @@ template <typename T> __device__ __forceinline__ T shfl_down(T v, int d) {
         return o;
     }
 }
+template <typename T> __device__ __forceinline__ T shfl_xor(T v, int m) {
+    if constexpr (sizeof(T) == 8) {
+        u64 x;
+        memcpy(&x, &v, 8);
+        x = __shfl_xor_sync(0xFFFFFFFFu, x, m);
+        T o;
+        memcpy(&o, &x, 8);
+        return o;
+    } else {
+        u32 x = 0;
+        memcpy(&x, &v, sizeof(T));
+        x = __shfl_xor_sync(0xFFFFFFFFu, x, m);
+        T o;
+        memcpy(&o, &x, sizeof(T));
+        return o;
+    }
+}
 template <typename T> __device__ __forceinline__ T shfl_idx(T v, int src) {
     if constexpr (sizeof(T) == 8) {
         u64 x;
@@ -254,7 +279,8 @@ template <typename Op, typename T> __device__ __forceinline__ T warp_scan_inclus
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
         T up = shfl_up(v, d);
-        if (lane >= (u32)d) v = Op::template apply<T>(up, v);
+        up = lane >= (u32)d ? up : Op::template identity<T>();
+        v = Op::template apply<T>(up, v);
     }
     return v;
 }

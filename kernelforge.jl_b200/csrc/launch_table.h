@@ -14,9 +14,10 @@ struct LaunchRow {
 };
 static const LaunchRow kLaunchTable[] = {
     {0, 0, 18446744073709551615ull, 256, 4, 8},
-    {1, 0, 18446744073709551615ull, 512, 4, 0},
+    {1, 0, 16777216ull, 512, 4, 0},
+    {1, 0, 18446744073709551615ull, 768, 4, 0},
     {2, 0, 18446744073709551615ull, 512, 16, 0},
     {3, 0, 18446744073709551615ull, 512, 16, 0},
 };
-static const int kNumLaunchRows = 4;
+static const int kNumLaunchRows = 5;
 }  // namespace kf

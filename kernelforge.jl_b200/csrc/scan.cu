@@ -1,10 +1,10 @@
 // Host entry points of the inclusive scan (C ABI): launch geometry, workspace layout, dtype dispatch.
 // The kernels live in scan_impl.cuh and are instantiated per element type in scan_inst_*.cu.
-#include "scan_impl.cuh"
+#include "scan_launch.cuh"
 
 namespace kf {
 
-int scan_plan(int elem_bytes, int epv, u64 n, const kf_launch_cfg *cfg, ScanPlan *plan) {
+int scan_plan(int elem_bytes, int epv, int narr, u64 n, const kf_launch_cfg *cfg, ScanPlan *plan) {
     kf_launch_cfg t;
     kf_launch_table_lookup(KF_PRIM_SCAN, elem_bytes, n, &t);
     if (cfg) {
@@ -16,8 +16,15 @@ int scan_plan(int elem_bytes, int epv, u64 n, const kf_launch_cfg *cfg, ScanPlan
         if (kScanVariants[i].threads == t.threads && kScanVariants[i].vecs == t.items) v = i;
     if (v < 0) return KF_ERR_UNSUPPORTED;
     plan->variant = v;
-    plan->tile = (u64)t.threads * t.items * epv;
-    plan->ntiles = 1 + (n + plan->tile - 1) / plan->tile;  // +1: a possible short head tile
+    plan->tile = scan_tile_elems(v, epv, narr);
+    // A ring variant may fall back to the direct kernel (smaller tiles) when the arrays turn out to
+    // be misaligned: size the descriptors for the smaller of the two tiles. +1: a short head tile.
+    u64 sizing_tile = plan->tile;
+    if (kScanVariants[v].ring) {
+        const u64 fb = scan_tile_elems(kScanFallbackVariant, epv, narr);
+        if (fb < sizing_tile) sizing_tile = fb;
+    }
+    plan->ntiles = 1 + (n + sizing_tile - 1) / sizing_tile;
     plan->words = elem_bytes <= 4 ? 1 : 2;
     if (plan->ntiles >= (1ull << 31)) return KF_ERR_INVALID_ARG;
     return KF_OK;
@@ -27,7 +34,7 @@ static size_t scan_ws_bytes(const ScanPlan &p) { return kHeaderBytes + align_up(
 
 // Fills the geometry that depends on the actual pointers: the shared 16-byte misalignment (if
 // any) becomes a short head tile, otherwise every tile takes the element-wise path.
-static void scan_geometry(const ScanPlan &p, u64 n, int elem_bytes, const uintptr_t *ptrs, int nptrs,
+static void scan_geometry(ScanPlan &p, u64 n, int elem_bytes, int epv, int narr, const uintptr_t *ptrs, int nptrs,
                           ScanArgs *a) {
     const uintptr_t mis = ptrs[0] & 15u;
     bool same = (mis % elem_bytes) == 0;
@@ -38,6 +45,10 @@ static void scan_geometry(const ScanPlan &p, u64 n, int elem_bytes, const uintpt
     a->n = n;
     a->vec_ok = same ? 1 : 0;
     a->head = same ? head : 0;
+    if (!same && kScanVariants[p.variant].ring) {  // the bulk-copy path needs 16-byte aligned arrays
+        p.variant = kScanFallbackVariant;
+        p.tile = scan_tile_elems(p.variant, epv, narr);
+    }
     const u64 first = a->head > 0 ? 1 : 0;
     a->ntiles = first + (n - a->head + p.tile - 1) / p.tile;
 }
@@ -50,9 +61,9 @@ extern "C" size_t kf_scan_workspace_bytes(int32_t dtype, int32_t pair, uint64_t 
     const int eb = pair ? 8 : dtype_bytes(dtype);
     if (eb == 0 || (pair && dtype != KF_F32)) return 0;
     ScanPlan p;
-    // The two-array affine layout packs 4 pairs per slot, the other layouts 16/elem_bytes
-    // elements; size for the smaller tile (more tiles) so one workspace fits both layouts.
-    if (scan_plan(eb, 16 / eb, n, cfg, &p) != KF_OK) return 0;
+    // The interleaved pair layout has the smallest tiles (2 pairs per 16-byte vector), so its size
+    // also covers the two-array layout.
+    if (scan_plan(eb, 16 / eb, 1, n, cfg, &p) != KF_OK) return 0;
     return scan_ws_bytes(p);
 }
 
@@ -68,17 +79,18 @@ extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t dtype, const void *src
     if (((uintptr_t)src % eb) || ((uintptr_t)dst % eb) || ((uintptr_t)ws % 256) || (init && ((uintptr_t)init % eb)))
         return KF_ERR_INVALID_ARG;
     ScanPlan p;
-    int rc = scan_plan(eb, 16 / eb, n, cfg, &p);
+    int rc = scan_plan(eb, 16 / eb, 1, n, cfg, &p);
     if (rc != KF_OK) return rc;
     if (ws_bytes < scan_ws_bytes(p)) return KF_ERR_WORKSPACE_TOO_SMALL;
 
     ScanArgs a;
     const uintptr_t ptrs[2] = {(uintptr_t)src, (uintptr_t)dst};
-    scan_geometry(p, n, eb, ptrs, 2, &a);
+    scan_geometry(p, n, eb, 16 / eb, 1, ptrs, 2, &a);
     a.header = (u32 *)ws;
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
     a.init = init;
     a.f = f;
+    a.block_order = cfg ? (cfg->reserved & 1) : 0;
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     switch (dtype) {
@@ -105,20 +117,18 @@ extern "C" int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, fl
     for (int i = 0; i < 4; ++i)
         if (ptrs[i] % 4) return KF_ERR_INVALID_ARG;
     if (((uintptr_t)ws % 256) || (init_ab && ((uintptr_t)init_ab % 4))) return KF_ERR_INVALID_ARG;
-    ScanPlan p, psize;
-    int rc = scan_plan(8, 4, n, cfg, &p);
-    if (rc != KF_OK) return rc;
-    rc = scan_plan(8, 2, n, cfg, &psize);  // the size kf_scan_workspace_bytes reports
+    ScanPlan p;
+    int rc = scan_plan(8, 4, 2, n, cfg, &p);
     if (rc != KF_OK) return rc;
     if (ws_bytes < scan_ws_bytes(p)) return KF_ERR_WORKSPACE_TOO_SMALL;
-    (void)psize;
 
     ScanArgs a;
-    scan_geometry(p, n, 4, ptrs, 4, &a);
+    scan_geometry(p, n, 4, 4, 2, ptrs, 4, &a);
     a.header = (u32 *)ws;
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
     a.init = init_ab;
     a.f = KF_MAP_IDENTITY;
+    a.block_order = cfg ? (cfg->reserved & 1) : 0;
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     return scan_dispatch_affine_soa(p.variant, a_src, b_src, a_dst, b_dst, a, s);
@@ -132,17 +142,18 @@ extern "C" int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64
         (init_ab && ((uintptr_t)init_ab % 4)))
         return KF_ERR_INVALID_ARG;
     ScanPlan p;
-    int rc = scan_plan(8, 2, n, cfg, &p);
+    int rc = scan_plan(8, 2, 1, n, cfg, &p);
     if (rc != KF_OK) return rc;
     if (ws_bytes < scan_ws_bytes(p)) return KF_ERR_WORKSPACE_TOO_SMALL;
 
     ScanArgs a;
     const uintptr_t ptrs[2] = {(uintptr_t)ab_src, (uintptr_t)ab_dst};
-    scan_geometry(p, n, 8, ptrs, 2, &a);
+    scan_geometry(p, n, 8, 2, 1, ptrs, 2, &a);
     a.header = (u32 *)ws;
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
     a.init = init_ab;
     a.f = KF_MAP_IDENTITY;
+    a.block_order = cfg ? (cfg->reserved & 1) : 0;
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     return scan_dispatch_affine_aos(p.variant, ab_src, ab_dst, a, s);

@@ -24,6 +24,8 @@
 
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace kf {
 
 enum : u32 { kInvalid = 0, kAggregate = 1, kPrefix = 2, kPoison = 3 };
@@ -134,50 +136,304 @@ struct ScanArgs {
     const void *init;  // optional left seed (one element) or nullptr
     int vec_ok;     // all arrays share their 16-byte misalignment: full tiles use 128-bit accesses
     int f;
+    int block_order;  // experiment: tile id = blockIdx.x instead of an atomic ticket
+#ifdef KF_SCAN_TRACE
+    u64 *trace;       // lab builds only: 16 words per tile of phase timestamps
+#endif
 };
 
-// Look-back over the descriptors of tiles [0, tile), by one full warp. Returns false if the wait
-// ran out or a predecessor was poisoned. On success `excl` (valid in every lane) is the
-// combination of all predecessors in order.
-template <typename T, typename Op>
-__device__ __forceinline__ bool lookback(const u64 *desc, u64 tile, u32 lane, T &excl, bool &timed_out) {
-    T acc = Op::template identity<T>();
-    long long cur = (long long)tile - 1;
-    u32 spins = 0;
-    timed_out = false;
-    while (true) {
-        const long long mine = cur - (long long)lane;
-        T v = Op::template identity<T>();
-        u32 st = kPrefix;  // lanes before tile 0 read as "prefix = identity"
-        if (mine >= 0) st = Desc<T>::read(desc, (u64)mine, v);
-        const u32 poison = __ballot_sync(0xFFFFFFFFu, st == kPoison);
-        if (poison) return false;
-        const u32 pfx = __ballot_sync(0xFFFFFFFFu, st == kPrefix);
-        const u32 inv = __ballot_sync(0xFFFFFFFFu, st == kInvalid);
-        const int last = pfx ? (__ffs(pfx) - 1) : 31;  // nearest tile with a full prefix
-        const u32 need = last == 31 ? 0xFFFFFFFFu : ((2u << last) - 1u);
-        if (inv & need) {
-            if (++spins > kSpinLimit) {
-                timed_out = true;
-                return false;
-            }
-            if (spins > 8) __nanosleep(spins > 64 ? 256 : 32);
-            continue;
+#ifdef KF_SCAN_TRACE
+__device__ __forceinline__ u64 kf_now() {
+    u64 t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define KF_TRACE(slot, val) do { if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) args.trace[tile * 16 + (slot)] = (val); } while (0)
+#else
+#define KF_TRACE(slot, val) do { } while (0)
+#endif
+
+// Scans the VECS x EPV elements a thread holds (in place, inclusive within each slot) and the slot
+// totals across the warp. On return e[j][k] is inclusive within its slot, slot_excl[j] is the
+// combination of everything the warp holds before slot j of this lane, and the return value is
+// the warp total (valid in every lane).
+template <typename T, typename Op, int VECS, int EPV>
+__device__ __forceinline__ T warp_tile_scan(T (&e)[VECS][EPV], T (&slot_excl)[VECS], u32 lane) {
+    T incl[VECS];
+#pragma unroll
+    for (int j = 0; j < VECS; ++j) {
+#pragma unroll
+        for (int k = 1; k < EPV; ++k) e[j][k] = Op::template apply<T>(e[j][k - 1], e[j][k]);
+        incl[j] = e[j][EPV - 1];
+    }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+        for (int j = 0; j < VECS; ++j) {  // VECS independent shuffles per step, no branches
+            T up = shfl_up(incl[j], d);
+            up = lane >= (u32)d ? up : Op::template identity<T>();
+            incl[j] = Op::template apply<T>(up, incl[j]);
         }
-        // Ordered fold of lanes 0..last: a higher lane is an earlier tile, i.e. the left operand.
-        T x = (int)lane <= last ? v : Op::template identity<T>();
+    }
+    // Exclusive prefix of each slot within the warp: carry over rows j, then lanes before mine.
+    T carry = Op::template identity<T>();
+#pragma unroll
+    for (int j = 0; j < VECS; ++j) {
+        T prev = shfl_up(incl[j], 1);
+        prev = lane == 0 ? Op::template identity<T>() : prev;
+        slot_excl[j] = Op::template apply<T>(carry, prev);
+        carry = Op::template apply<T>(carry, shfl_idx(incl[j], 31));
+    }
+    return carry;
+}
+
+// out[i] = in[(i + amount) mod N] for a lane-dependent amount, N a power of two: log2(N) stages of
+// selects, no dynamic register indexing.
+template <typename T, int N> __device__ __forceinline__ void rotate_regs(T (&x)[N], u32 amount) {
+#pragma unroll
+    for (int s = 1; s < N; s <<= 1) {
+        T y[N];
+        const bool on = (amount & s) != 0;
+#pragma unroll
+        for (int i = 0; i < N; ++i) y[i] = on ? x[(i + s) & (N - 1)] : x[i];
+#pragma unroll
+        for (int i = 0; i < N; ++i) x[i] = y[i];
+    }
+}
+
+// Blocked variant of the in-register tile scan, for data staged in shared memory. A thread owns
+// VECS CONSECUTIVE 16-byte slots (lane l of a warp: slots VECS*l .. VECS*l+VECS-1 of the warp's
+// run), so one warp scan covers VECS*EPV elements per thread instead of EPV. To keep the 128-bit
+// shared-memory accesses free of bank conflicts the thread touches its slots in a rotated order:
+// register j holds slot (j + rot) mod VECS, rot = blocked_rot(lane). On return r[j][k] is inclusive
+// within the WARP; the return value is the warp total (valid in every lane).
+template <int VECS> __device__ __forceinline__ u32 blocked_rot(u32 lane) {
+    static_assert(VECS == 2 || VECS == 4 || VECS == 8, "rotation scheme covers 2, 4 and 8 slots per thread");
+    return (lane >> (VECS == 8 ? 0 : (VECS == 4 ? 1 : 2))) & (VECS - 1);
+}
+template <typename T, typename Op, int VECS, int EPV>
+__device__ __forceinline__ T warp_tile_scan_blocked(T (&r)[VECS][EPV], u32 rot, u32 lane) {
+    T tot[VECS];
+#pragma unroll
+    for (int j = 0; j < VECS; ++j) {
+#pragma unroll
+        for (int k = 1; k < EPV; ++k) r[j][k] = Op::template apply<T>(r[j][k - 1], r[j][k]);
+        tot[j] = r[j][EPV - 1];
+    }
+    rotate_regs<T, VECS>(tot, (VECS - rot) & (VECS - 1));  // tot[m]: total of the thread's m-th slot
+    T excl[VECS];
+    excl[0] = Op::template identity<T>();
+#pragma unroll
+    for (int m = 1; m < VECS; ++m) excl[m] = Op::template apply<T>(excl[m - 1], tot[m - 1]);
+    const T thread_total = Op::template apply<T>(excl[VECS - 1], tot[VECS - 1]);
+    T incl = thread_total;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        T up = shfl_up(incl, d);
+        up = lane >= (u32)d ? up : Op::template identity<T>();
+        incl = Op::template apply<T>(up, incl);
+    }
+    T before = shfl_up(incl, 1);
+    before = lane == 0 ? Op::template identity<T>() : before;
+    rotate_regs<T, VECS>(excl, rot);  // excl[j]: prefix of the slot register j holds
+#pragma unroll
+    for (int j = 0; j < VECS; ++j) {
+        const T p = Op::template apply<T>(before, excl[j]);
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) r[j][k] = Op::template apply<T>(p, r[j][k]);
+    }
+    return shfl_idx(incl, 31);
+}
+
+// Striped in-register tile scan whose cross-lane step goes through a small per-warp scratch in
+// shared memory: the VECS*32 slot totals of a warp are written in element order (v, lane), each
+// lane then takes VECS CONSECUTIVE totals, scans them sequentially, ONE warp scan combines the 32
+// lane sums, and the exclusive prefixes travel back the same way. Same result as warp_tile_scan
+// (e[v][k] inclusive within the warp afterwards, not only within the slot) for about a third of
+// the instructions, and the registers stay striped, so global stores stay coalesced.
+// `scratch` holds VECS*32 elements of T per warp. Returns the warp total (valid in every lane).
+template <typename T, typename Op, int VECS, int EPV>
+__device__ __forceinline__ T warp_tile_scan_via_smem(T (&e)[VECS][EPV], T *scratch, u32 lane) {
+#pragma unroll
+    for (int v = 0; v < VECS; ++v) {
+#pragma unroll
+        for (int k = 1; k < EPV; ++k) e[v][k] = Op::template apply<T>(e[v][k - 1], e[v][k]);
+        scratch[v * 32 + lane] = e[v][EPV - 1];
+    }
+    __syncwarp();
+    T c[VECS];
+#pragma unroll
+    for (int i = 0; i < VECS; ++i) c[i] = scratch[lane * VECS + i];
+#pragma unroll
+    for (int i = 1; i < VECS; ++i) c[i] = Op::template apply<T>(c[i - 1], c[i]);
+    T incl = c[VECS - 1];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        T up = shfl_up(incl, d);
+        up = lane >= (u32)d ? up : Op::template identity<T>();
+        incl = Op::template apply<T>(up, incl);
+    }
+    T before = shfl_up(incl, 1);
+    before = lane == 0 ? Op::template identity<T>() : before;
+    scratch[lane * VECS] = before;
+#pragma unroll
+    for (int i = 1; i < VECS; ++i) scratch[lane * VECS + i] = Op::template apply<T>(before, c[i - 1]);
+    __syncwarp();
+#pragma unroll
+    for (int v = 0; v < VECS; ++v) {
+        const T p = scratch[v * 32 + lane];
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) e[v][k] = Op::template apply<T>(p, e[v][k]);
+    }
+    __syncwarp();  // the scratch may be reused right away
+    return shfl_idx(incl, 31);
+}
+
+// CTA-wide barrier, or a named barrier over the first BAR_THREADS threads when part of the CTA
+// (a producer warp) must not take part.
+template <int BAR_THREADS> __device__ __forceinline__ void cta_sync() {
+    if constexpr (BAR_THREADS == 0) __syncthreads();
+    else asm volatile("bar.sync 1, %0;" ::"n"(BAR_THREADS) : "memory");
+}
+
+// What one warp's window of 32 predecessor descriptors looks like, for the block-wide look-back.
+enum : u32 { kLbAllAgg = 0, kLbHasPrefix = 1, kLbNotReady = 2, kLbPoison = 3 };
+
+// Combination of the values of lanes 0..31 in DESCENDING lane order (lane 31 is the leftmost
+// operand), valid in every lane. Look-back windows are laid out with the nearest predecessor in
+// lane 0, so descending lane order is array order. Commutative operators use a butterfly (or one
+// redux.sync for 32-bit integer add/min/max/and/or/xor); the others keep the ordered tree.
+template <typename T, typename Op> __device__ __forceinline__ T warp_fold_descending(T x, u32 lane) {
+    if constexpr (Op::commutative) {
+        if constexpr (sizeof(T) == 4 && !IsFloat<T>::value && !std::is_same<Op, OpMul>::value) {
+            if constexpr (std::is_same<Op, OpAdd>::value) return (T)__reduce_add_sync(0xFFFFFFFFu, (unsigned)x);
+            else if constexpr (std::is_same<Op, OpAnd>::value) return (T)__reduce_and_sync(0xFFFFFFFFu, (unsigned)x);
+            else if constexpr (std::is_same<Op, OpOr>::value) return (T)__reduce_or_sync(0xFFFFFFFFu, (unsigned)x);
+            else if constexpr (std::is_same<Op, OpXor>::value) return (T)__reduce_xor_sync(0xFFFFFFFFu, (unsigned)x);
+            else if constexpr (std::is_same<Op, OpMin>::value) return (T)__reduce_min_sync(0xFFFFFFFFu, x);
+            else return (T)__reduce_max_sync(0xFFFFFFFFu, x);
+        } else {
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) x = Op::template apply<T>(x, shfl_xor(x, d));
+            return x;
+        }
+    } else {
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             T y = shfl_down(x, d);
-            if (lane + d < 32) x = Op::template apply<T>(y, x);
+            y = lane + d < 32 ? y : Op::template identity<T>();
+            x = Op::template apply<T>(y, x);
         }
-        x = shfl_idx(x, 0);
-        acc = Op::template apply<T>(x, acc);
-        if (pfx) break;
-        cur -= 32;
+        return shfl_idx(x, 0);
     }
-    excl = acc;
-    return true;
+}
+
+// Block-wide look-back, first half: every warp summarises its window of 32 predecessor descriptors
+// (one per lane, read earlier: warp w covers tiles tile-1-32w .. tile-32-32w) into s_info[warp] /
+// s_val[warp]. A barrier must separate it from the second half.
+template <typename T, typename Op>
+__device__ __forceinline__ void lookback_summarise(u64 tile, u32 st, T v, u32 warp, u32 lane, u32 *s_info, T *s_val) {
+    const long long mine = (long long)tile - 1 - (long long)(warp * 32 + lane);
+    if (mine < 0) st = kPrefix;  // positions before tile 0 read as "prefix = identity"
+    const u32 poison = __ballot_sync(0xFFFFFFFFu, st == kPoison);
+    const u32 pfx = __ballot_sync(0xFFFFFFFFu, st == kPrefix);
+    const u32 inv = __ballot_sync(0xFFFFFFFFu, st == kInvalid);
+    const int last = pfx ? (__ffs(pfx) - 1) : 31;  // nearest tile of the window with an inclusive prefix
+    const u32 need = last == 31 ? 0xFFFFFFFFu : ((2u << last) - 1u);
+    const T x = ((int)lane <= last && mine >= 0) ? v : Op::template identity<T>();
+    const T folded = warp_fold_descending<T, Op>(x, lane);
+    if (lane == 0) {
+        s_info[warp] = poison ? kLbPoison : ((inv & need) ? kLbNotReady : (pfx ? kLbHasPrefix : kLbAllAgg));
+        s_val[warp] = folded;
+    }
+}
+// Second half, run by every warp on the same summaries: 1 = resolved (`excl`, valid in every thread,
+// combines everything back to and including the nearest prefix); 0 = the caller has to poll
+// (someone was not ready, or no prefix within 32*WARPS tiles; for the latter `excl` holds the
+// aggregates of the whole block window); 2 = a predecessor was poisoned.
+template <typename T, typename Op, int WARPS>
+__device__ __forceinline__ int lookback_finish(u32 lane, const u32 *s_info, const T *s_val, T &excl, bool &all_aggregates) {
+    static_assert(WARPS <= 32, "one lane per warp in the final fold");
+    const u32 info = lane < (u32)WARPS ? s_info[lane] : (u32)kLbAllAgg;
+    const T val = lane < (u32)WARPS ? s_val[lane] : Op::template identity<T>();
+    const u32 not_agg = __ballot_sync(0xFFFFFFFFu, info != kLbAllAgg);
+    all_aggregates = not_agg == 0;
+    const int stop = all_aggregates ? 31 : __ffs(not_agg) - 1;
+    const u32 why = all_aggregates ? (u32)kLbAllAgg : __shfl_sync(0xFFFFFFFFu, info, stop);
+    if (why == kLbPoison) return 2;
+    if (why == kLbNotReady) return 0;
+    const T y = (int)lane <= stop ? val : Op::template identity<T>();
+    excl = warp_fold_descending<T, Op>(y, lane);
+    return all_aggregates ? 0 : 1;
+}
+
+// Block-wide look-back with polling: the CTA's WARPS warps read WARPS consecutive windows of 32
+// predecessor descriptors in the same round trip, so a tile whose nearest inclusive prefix is
+// hundreds of tiles back still resolves in one poll instead of walking 32 tiles per round trip.
+// Called by every thread that takes part in barrier BAR_THREADS (it synchronises). On success the
+// exclusive prefix is returned in every thread and thread 0 has published the tile's inclusive
+// prefix; on failure (bounded wait ran out, or a poisoned predecessor) thread 0 has published
+// poison, recorded the error and raised *s_abort, and the function returns false after a barrier.
+// `s_info` / `s_val` hold one entry per warp. PUBLISH_AGG = false when the caller has already
+// published the tile's aggregate.
+template <typename T> __device__ __forceinline__ u32 lookback_read(const ScanArgs &args, u64 base_tile, u32 warp, u32 lane, T &v) {
+    const long long mine = (long long)base_tile - 1 - (long long)(warp * 32 + lane);
+    v = T();
+    return mine >= 0 ? Desc<T>::read(args.desc, (u64)mine, v) : (u32)kPrefix;
+}
+
+template <typename T, typename Op, int WARPS, bool PUBLISH_AGG, int BAR_THREADS>
+__device__ __forceinline__ bool resolve_tile_prefix_block(const ScanArgs &args, u64 tile, T tile_total, u32 warp, u32 lane,
+                                                          int *s_abort, u32 *s_info, T *s_val, T &excl_out) {
+    const u32 tid = threadIdx.x;
+    if (tile == 0) {
+        T excl = Op::template identity<T>();
+        if (args.init) excl = *reinterpret_cast<const T *>(args.init);
+        if (tid == 0) Desc<T>::publish(args.desc, tile, kPrefix, Op::template apply<T>(excl, tile_total));
+        excl_out = excl;
+        return true;
+    }
+    if (PUBLISH_AGG && tid == 0) Desc<T>::publish(args.desc, tile, kAggregate, tile_total);
+    T acc = Op::template identity<T>();
+    u64 base = tile;  // the window covers tiles base-1 .. base-32*WARPS
+    u32 spins = 0;
+    int how;
+    bool timed_out = false;
+    while (true) {
+        T v;
+        const u32 st = lookback_read<T>(args, base, warp, lane, v);
+        lookback_summarise<T, Op>(base, st, v, warp, lane, s_info, s_val);
+        cta_sync<BAR_THREADS>();
+        T part = Op::template identity<T>();
+        bool all_agg = false;
+        how = lookback_finish<T, Op, WARPS>(lane, s_info, s_val, part, all_agg);
+        cta_sync<BAR_THREADS>();  // summaries may be overwritten from here on
+        if (how == 1 || all_agg) acc = Op::template apply<T>(part, acc);
+        if (how != 0) break;
+        if (all_agg) {
+            base -= 32 * WARPS;  // nothing but aggregates in sight: keep walking back
+            spins = 0;
+        } else {
+            if (++spins > kSpinLimit) {
+                timed_out = true;
+                how = 2;
+                break;
+            }
+            if (spins > 4) __nanosleep(spins > 64 ? 256 : 32);
+        }
+    }
+    if (how == 1) {
+        if (tid == 0) Desc<T>::publish(args.desc, tile, kPrefix, Op::template apply<T>(acc, tile_total));
+        excl_out = acc;
+        return true;
+    }
+    if (tid == 0) {
+        if (timed_out) record_error(args.header, KF_ERR_TIMEOUT, (u32)tile);
+        Desc<T>::publish(args.desc, tile, kPoison, Op::template identity<T>());
+        *s_abort = 1;
+    }
+    cta_sync<BAR_THREADS>();
+    return false;
 }
 
 template <typename T, typename Op, typename Access, int THREADS, int VECS>
@@ -187,19 +443,23 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
     constexpr u64 TILE = (u64)THREADS * VECS * EPV;
 
     __shared__ T s_warp_total[WARPS];
-    __shared__ T s_tile_excl;
     __shared__ u64 s_tile;
     __shared__ int s_abort;
+    __shared__ u32 s_lb_info[WARPS];
+    __shared__ T s_lb_val[WARPS];
 
     const u32 tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
 
     if (tid == 0) {
-        s_tile = (u64)atomicAdd(&args.header[kTicketBase], 1u);
+        s_tile = args.block_order ? (u64)blockIdx.x : (u64)atomicAdd(&args.header[kTicketBase], 1u);
         s_abort = ld_relaxed_u32(&args.header[kStatusWord]) != 0u;
     }
     __syncthreads();
     const u64 tile = s_tile;
     if (tile >= args.ntiles) return;
+#ifdef KF_SCAN_TRACE
+    KF_TRACE(0, kf_now());
+#endif
     if (s_abort) {  // an earlier tile failed: pass the poison on so nobody waits for this tile
         if (tid == 0) Desc<T>::publish(args.desc, tile, kPoison, Op::template identity<T>());
         return;
@@ -238,33 +498,13 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
     }
 
     // ---- thread-local scan of each slot, warp scan of slot totals ----------------------------
-    T incl[VECS];
-#pragma unroll
-    for (int j = 0; j < VECS; ++j) {
-#pragma unroll
-        for (int k = 1; k < EPV; ++k) e[j][k] = Op::template apply<T>(e[j][k - 1], e[j][k]);
-        incl[j] = e[j][EPV - 1];
-    }
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-#pragma unroll
-        for (int j = 0; j < VECS; ++j) {  // VECS independent shuffles per step
-            T up = shfl_up(incl[j], d);
-            if (lane >= (u32)d) incl[j] = Op::template apply<T>(up, incl[j]);
-        }
-    }
-    // Exclusive prefix of each slot within the warp: carry over rows j, then lanes before mine.
     T slot_excl[VECS];
-    T carry = Op::template identity<T>();
-#pragma unroll
-    for (int j = 0; j < VECS; ++j) {
-        T prev = shfl_up(incl[j], 1);
-        if (lane == 0) prev = Op::template identity<T>();
-        slot_excl[j] = Op::template apply<T>(carry, prev);
-        carry = Op::template apply<T>(carry, shfl_idx(incl[j], 31));
-    }
+    const T carry = warp_tile_scan<T, Op, VECS, EPV>(e, slot_excl, lane);
     if (lane == 0) s_warp_total[warp] = carry;
     __syncthreads();
+#ifdef KF_SCAN_TRACE
+    KF_TRACE(1, kf_now());
+#endif
 
     // ---- warp prefix within the tile and the tile aggregate ----------------------------------
     T warp_excl = Op::template identity<T>();
@@ -272,36 +512,16 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
         const T t = s_warp_total[w];
-        if (w < (int)warp) warp_excl = Op::template apply<T>(warp_excl, t);
+        warp_excl = Op::template apply<T>(warp_excl, w < (int)warp ? t : Op::template identity<T>());
         tile_total = Op::template apply<T>(tile_total, t);
     }
 
     // ---- publish, look back, publish ---------------------------------------------------------
-    if (warp == 0) {
-        T excl = Op::template identity<T>();
-        bool ok = true, timed_out = false;
-        if (tile == 0) {
-            if (args.init) excl = *reinterpret_cast<const T *>(args.init);
-        } else {
-            if (lane == 0) Desc<T>::publish(args.desc, tile, kAggregate, tile_total);
-            ok = lookback<T, Op>(args.desc, tile, lane, excl, timed_out);
-        }
-        if (lane == 0) {
-            if (ok) {
-                Desc<T>::publish(args.desc, tile, kPrefix, Op::template apply<T>(excl, tile_total));
-                s_tile_excl = excl;
-            } else {
-                if (timed_out) record_error(args.header, KF_ERR_TIMEOUT, (u32)tile);
-                Desc<T>::publish(args.desc, tile, kPoison, Op::template identity<T>());
-                s_abort = 1;
-            }
-        }
-    }
-    __syncthreads();
-    if (s_abort) return;
+    T tile_excl;
+    if (!resolve_tile_prefix_block<T, Op, WARPS, true, 0>(args, tile, tile_total, warp, lane, &s_abort, s_lb_info, s_lb_val, tile_excl)) return;
 
     // ---- apply the prefix and store -----------------------------------------------------------
-    const T base = Op::template apply<T>(s_tile_excl, warp_excl);
+    const T base = Op::template apply<T>(tile_excl, warp_excl);
     if (fast) {
 #pragma unroll
         for (int j = 0; j < VECS; ++j) {
@@ -322,80 +542,5 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
         }
     }
 }
-
-// ---- host-side geometry shared by the workspace query and the launch ---------------------------
-struct ScanVariant {
-    int threads, vecs;
-};
-static const ScanVariant kScanVariants[] = {{256, 4}, {512, 4}, {512, 2}, {1024, 2}};
-constexpr int kNumScanVariants = 4;
-
-struct ScanPlan {
-    int variant;
-    u64 tile;     // elements per tile
-    u64 ntiles;   // upper bound used for sizing (includes a possible head tile)
-    int words;    // descriptor words per tile
-};
-
-int scan_plan(int elem_bytes, int epv, u64 n, const kf_launch_cfg *cfg, ScanPlan *plan);
-
-template <typename T, typename Op, typename Access>
-int scan_launch(int variant, const Access &acc, const ScanArgs &args, cudaStream_t s) {
-    const unsigned grid = (unsigned)args.ntiles;
-    switch (variant) {
-    case 0: scan_kernel<T, Op, Access, 256, 4><<<grid, 256, 0, s>>>(acc, args); break;
-    case 1: scan_kernel<T, Op, Access, 512, 4><<<grid, 512, 0, s>>>(acc, args); break;
-    case 2: scan_kernel<T, Op, Access, 512, 2><<<grid, 512, 0, s>>>(acc, args); break;
-    case 3: scan_kernel<T, Op, Access, 1024, 2><<<grid, 1024, 0, s>>>(acc, args); break;
-    default: return KF_ERR_UNSUPPORTED;
-    }
-    KF_CUDA_TRY(cudaGetLastError());
-    return KF_OK;
-}
-
-// One translation unit per element type instantiates this (keeps the build parallel).
-template <typename T>
-int scan_dispatch_ops(int op, int variant, const PlainAccess<T> &acc, const ScanArgs &args, cudaStream_t s) {
-    switch (op) {
-    case KF_OP_ADD: return scan_launch<T, OpAdd>(variant, acc, args, s);
-    case KF_OP_MUL: return scan_launch<T, OpMul>(variant, acc, args, s);
-    case KF_OP_MIN: return scan_launch<T, OpMin>(variant, acc, args, s);
-    case KF_OP_MAX: return scan_launch<T, OpMax>(variant, acc, args, s);
-    default: break;
-    }
-    if constexpr (!IsFloat<T>::value) {
-        switch (op) {
-        case KF_OP_AND: return scan_launch<T, OpAnd>(variant, acc, args, s);
-        case KF_OP_OR: return scan_launch<T, OpOr>(variant, acc, args, s);
-        case KF_OP_XOR: return scan_launch<T, OpXor>(variant, acc, args, s);
-        default: break;
-        }
-    }
-    return KF_ERR_UNSUPPORTED;
-}
-
-// Defined in scan_inst_*.cu
-int scan_dispatch_u8(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_i8(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_u16(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_i16(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_u32(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_i32(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_u64(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_i64(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_f32(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_f64(int op, int variant, const void *src, void *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_affine_aos(int variant, const float *src, float *dst, const ScanArgs &args, cudaStream_t s);
-int scan_dispatch_affine_soa(int variant, const float *a_src, const float *b_src, float *a_dst, float *b_dst,
-                             const ScanArgs &args, cudaStream_t s);
-
-#define KF_SCAN_INSTANTIATE(NAME, T)                                                                     \
-    namespace kf {                                                                                       \
-    int scan_dispatch_##NAME(int op, int variant, const void *src, void *dst, const ScanArgs &args,      \
-                             cudaStream_t s) {                                                           \
-        PlainAccess<T> acc{(const T *)src, (T *)dst};                                                    \
-        return scan_dispatch_ops<T>(op, variant, acc, args, s);                                          \
-    }                                                                                                    \
-    }
 
 }  // namespace kf

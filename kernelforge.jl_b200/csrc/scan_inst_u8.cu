@@ -1,4 +1,4 @@
 // Scan kernels for element type uint8_t (one translation unit per type keeps the build parallel).
-#include "scan_impl.cuh"
+#include "scan_launch.cuh"
 
 KF_SCAN_INSTANTIATE(u8, uint8_t)

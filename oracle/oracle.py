@@ -174,7 +174,7 @@ def np_scan(f: int, op: int, x: np.ndarray) -> np.ndarray:
     x = _c(x)
     y = np_map(f, x.astype(np.float64) if x.dtype.kind == "f" else x)
     with np.errstate(over="ignore"):
-        return _NP_OPS[op].accumulate(y)
+        return _NP_OPS[op].accumulate(y, dtype=y.dtype)  # keep the element type: integers wrap
 
 
 def np_mapreduce(f: int, op: int, x: np.ndarray):

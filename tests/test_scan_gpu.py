@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import assert_close_rel, scan_tol, to_dev, to_host
+from util import assert_close_rel, pow2_factors, scan_tol, to_dev, to_host
 
 pytestmark = pytest.mark.gpu
 
@@ -26,7 +26,7 @@ def _check_scan(kf, oracle, x, op, **kw):
             floor = np.cumsum(np.abs(x.astype(np.float64)))
             err = np.abs(got.astype(np.float64) - ref)
             assert (err <= scan_tol(x.size) * np.maximum(floor, 1e-300)).all(), float((err / floor).max())
-        elif op in ("min", "max"):
+        elif op in ("min", "max", "*"):  # `*` is tested on exact power-of-two factors
             assert (got.astype(np.float64) == ref).all()
         else:
             assert_close_rel(got, ref, x.size)
@@ -65,7 +65,7 @@ def test_dtype_op_matrix(kf, oracle, dtype, op):
     rng = np.random.default_rng(11)
     n = 70_003
     if np.dtype(dtype).kind == "f":
-        x = (1.0 + 1e-4 * rng.standard_normal(n)).astype(dtype) if op == "*" else rng.random(n).astype(dtype)
+        x = pow2_factors(n, rng, dtype) if op == "*" else rng.random(n).astype(dtype)
     else:
         info = np.iinfo(dtype)
         x = rng.integers(info.min, info.max, size=n, dtype=dtype, endpoint=True)
@@ -74,8 +74,12 @@ def test_dtype_op_matrix(kf, oracle, dtype, op):
 
 def test_float32_mul_long(kf, oracle):
     n = 1_000_000
-    x = np.exp(np.random.default_rng(5).standard_normal(n) * 1e-3).astype(np.float32)
+    x = pow2_factors(n, np.random.default_rng(5), np.float32)
     _check_scan(kf, oracle, x, "*")
+    x = np.random.default_rng(6).random(100_000).astype(np.float32) + 0.5  # generic factors: tolerance
+    got = to_host(kf.scan("*", to_dev(x[:500])))
+    ref = oracle.c_scan(0, 1, x[:500])
+    assert (np.abs(got - ref) <= 1e-4 * np.abs(ref)).all()
 
 
 @pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float32, np.float64])
@@ -92,10 +96,21 @@ def test_reused_tmp(kf, oracle, dtype, n):
         assert (to_host(dst) == np.cumsum(h, dtype=dtype)).all()  # small integers: exact in every type
 
 
-@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (512, 2), (1024, 2)])
+@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (256, 8), (128, 8), (768, 4), (992, 4)])
 def test_launch_variants(kf, oracle, workgroup, nitem):
+    """Every compiled variant: the direct kernels and the two persistent ring kernels (768, 992)."""
     x = np.random.default_rng(2).integers(0, 256, 3_000_017).astype(np.uint32)
     _check_scan(kf, oracle, x, "+", workgroup=workgroup, Nitem=nitem)
+    for dt in (np.uint8, np.float64):
+        y = np.random.default_rng(3).integers(0, 100, 1_500_011).astype(dt)
+        _check_scan(kf, oracle, y, "max" if dt == np.uint8 else "+", workgroup=workgroup, Nitem=nitem)
+    a, b = _affine_inputs(700_001, 5)
+    ra, rb = oracle.c_scan_affine(a, b)
+    da, db = kf.scan(kf.AffineCompose(), (to_dev(a), to_dev(b)), workgroup=workgroup, Nitem=nitem)
+    _check_affine(a.size, to_host(da), to_host(db), ra, rb)
+    ab = np.stack([a, b], axis=1).copy()
+    out = to_host(kf.scan(kf.AffineCompose(), to_dev(ab.reshape(-1)).view(a.size, 2), workgroup=workgroup, Nitem=nitem))
+    _check_affine(a.size, out[:, 0], out[:, 1], ra, rb)
     with pytest.raises(kf.ArgumentError):
         kf.scan("+", to_dev(x), workgroup=96, Nitem=3)
 

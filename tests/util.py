@@ -58,3 +58,13 @@ def assert_close_rel(got: np.ndarray, ref: np.ndarray, n: int, floor: float = 0.
 
 def bits(a: np.ndarray) -> np.ndarray:
     return np.ascontiguousarray(a).view("uint%d" % (a.dtype.itemsize * 8))
+
+
+def pow2_factors(n: int, rng, dtype) -> np.ndarray:
+    """Mostly 1.0 with up to 60 factors of 2.0 or 0.5: every product of any subset, in any
+    association order, is an exact power of two within 2^+-60, so `*` can be checked bit for bit."""
+    x = np.ones(n, dtype=dtype)
+    k = min(60, n)
+    pos = rng.choice(n, size=k, replace=False)
+    x[pos] = np.where(rng.integers(0, 2, k) == 0, 2.0, 0.5).astype(dtype)
+    return x
