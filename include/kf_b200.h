@@ -161,7 +161,8 @@ int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, float *a_dst,
                            uint64_t n, const float *init_ab,
                            void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 
-/* Same, array-of-structures: src/dst hold n interleaved (a, b) pairs (NTuple{2,Float32}). */
+/* Same, array-of-structures: src/dst hold n interleaved (a, b) pairs, i.e. the reference's
+ * scan!(op, dst, src) over a Vector{NTuple{2,Float32}} (src/scan/scan.jl:261-284). */
 int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab,
                            void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 

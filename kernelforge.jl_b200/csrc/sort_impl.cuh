@@ -8,8 +8,8 @@
 // what moves. For integer keys the map only changes the top byte, so it costs one XOR folded into
 // the digit mask (`top_xor`); float keys add a shift and one logic op per key for the complement.
 //
-// Ranking uses match.any: all lanes holding the same digit find each other in one instruction, the
-// lowest such lane bumps the warp's private digit counter once for the whole group, and every lane
+// Ranking matches digits across the warp (eight ballots per key): all lanes holding the same digit
+// find each other, the lowest such lane bumps the warp's private digit counter once for the whole group, and every lane
 // adds the count of lower lanes in its group. Ranks therefore follow element order for any data,
 // which is what makes each pass stable (shared-memory atomics alone would not guarantee it).
 //
@@ -54,6 +54,20 @@ template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT pad_key(
     // floats: a non-negative key keeps its bits -> the same pattern 0x7FFF...FF maps to all ones.
     KeyT all = (KeyT)~(KeyT)0;
     return signed_or_float ? (KeyT)(all >> 1) : all;
+}
+
+// Lanes of the warp that hold the same 8-bit digit as this one (its own bit included). Eight
+// ballots, one per digit bit: the hardware match.any instruction costs several hundred cycles on
+// 32 mostly distinct values, the ballots are independent of each other and of other keys.
+__device__ __forceinline__ u32 match_digit(u32 d) {
+    u32 peers = 0xFFFFFFFFu;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        const bool bit = (d >> b) & 1u;
+        const u32 m = __ballot_sync(0xFFFFFFFFu, bit);
+        peers &= bit ? m : ~m;
+    }
+    return peers;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -141,7 +155,21 @@ struct SortPassArgs {
     int shift;
     u32 top_xor;
     int signed_or_float;
+#ifdef KF_SORT_TRACE
+    u64 *trace;  // lab builds only: 8 words per tile
+#endif
 };
+
+#ifdef KF_SORT_TRACE
+__device__ __forceinline__ u64 kf_sort_now() {
+    u64 t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define KF_STRACE(slot) do { if (threadIdx.x == 0) a.trace[tile * 8 + (slot)] = kf_sort_now(); } while (0)
+#else
+#define KF_STRACE(slot) do { } while (0)
+#endif
 
 template <typename KeyT, typename ValT, int THREADS, int ITEMS> struct SortSmem {
     static constexpr int WARPS = THREADS / 32;
@@ -149,7 +177,7 @@ template <typename KeyT, typename ValT, int THREADS, int ITEMS> struct SortSmem 
     static constexpr bool HAS_VAL = !std::is_same<ValT, void>::value;
     using ValS = typename std::conditional<HAS_VAL, ValT, char>::type;  // storage type (unused without values)
     static constexpr size_t kWhist = (size_t)WARPS * kRadix * 4;
-    static constexpr size_t kGbase = (size_t)kRadix * 8;
+    static constexpr size_t kGbase = (size_t)kRadix * 16;  // global bases (u64) + digit counts + digit starts (u32)
     static constexpr size_t kKeys = (size_t)TILE * sizeof(KeyT);
     static constexpr size_t kVals = HAS_VAL ? (size_t)TILE * sizeof(ValS) : 0;
     static constexpr size_t kBytes = kWhist + kGbase + kKeys + kVals + 64;
@@ -165,6 +193,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
 
     extern __shared__ __align__(16) unsigned char smem[];
     u64 *s_gbase = reinterpret_cast<u64 *>(smem);                              // [256]
+    u32 *s_cnt = reinterpret_cast<u32 *>(smem + kRadix * 8);                   // [256] keys per digit (pads excluded)
+    u32 *s_dexcl = s_cnt + kRadix;                                             // [256] start of each digit's run
     u32 *s_whist = reinterpret_cast<u32 *>(smem + SM::kGbase);                 // [WARPS][256]
     KeyT *s_keys = reinterpret_cast<KeyT *>(smem + SM::kGbase + SM::kWhist);   // [TILE]
     ValS *s_vals = reinterpret_cast<ValS *>(smem + SM::kGbase + SM::kWhist + SM::kKeys);
@@ -194,6 +224,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         return;
     }
 
+    KF_STRACE(0);
     const u64 tile_start = tile * (u64)TILE;
     const u32 count = (u32)(a.n - tile_start < (u64)TILE ? a.n - tile_start : (u64)TILE);
     const bool full = count == (u32)TILE;
@@ -202,8 +233,9 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
     // ---- 1. load keys (warp-striped: item i of lane l is element warp_off + 32*i) ---------------
     KeyT key[ITEMS];
     if (full) {
+        const KeyT *p = kin + tile_start + warp_off;
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) key[i] = kin[tile_start + warp_off + i * 32];
+        for (int i = 0; i < ITEMS; ++i) key[i] = p[i * 32];
     } else {
         const KeyT pad = pad_key<KeyT, IS_FLOAT>(a.signed_or_float != 0);
 #pragma unroll
@@ -213,49 +245,82 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         }
     }
 
+    KF_STRACE(1);
     // ---- 2. rank each key within (warp, digit), in element order --------------------------------
+    // Batches of BATCH keys: all match.any first, then the leaders' shared-memory atomics (issued in
+    // item order, which is what keeps equal digits in element order), then the broadcasts. The three
+    // steps of one key depend on each other, the keys of a batch do not, so their latencies overlap.
     u32 rank[ITEMS];
     const u32 lt = lanemask_lt();
+    constexpr int BATCH = ITEMS % 8 == 0 ? 8 : ITEMS;
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        const u32 d = digit_of<KeyT, IS_FLOAT>(key[i], a.shift, a.top_xor);
-        const u32 peers = __match_any_sync(0xFFFFFFFFu, d);
-        const int leader = __ffs(peers) - 1;
-        u32 before = 0;
-        if ((int)lane == leader) before = atomicAdd(&my_hist[d], (u32)__popc(peers));
-        before = __shfl_sync(0xFFFFFFFFu, before, leader);
-        rank[i] = before + __popc(peers & lt);
+    for (int i0 = 0; i0 < ITEMS; i0 += BATCH) {
+        u32 before[BATCH];
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const u32 d = digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor);
+            const u32 peers = match_digit(d);
+            // lower lanes with my digit | leader lane << 8 | group size << 16
+            rank[i0 + i] = (u32)__popc(peers & lt) | ((u32)(__ffs(peers) - 1) << 8) | ((u32)__popc(peers) << 16);
+        }
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const u32 d = digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor);
+            before[i] = 0;
+            if (((rank[i0 + i] >> 8) & 0xFFu) == lane) before[i] = atomicAdd(&my_hist[d], rank[i0 + i] >> 16);
+        }
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const u32 b = __shfl_sync(0xFFFFFFFFu, before[i], (rank[i0 + i] >> 8) & 0xFFu);
+            rank[i0 + i] = b + (rank[i0 + i] & 0xFFu);
+        }
     }
     __syncthreads();
+    KF_STRACE(2);
+
+    // The look-back threads: one per digit. With 512 threads or more they are the second group of
+    // 256 threads, which has nothing to do in steps 3 and 4, so the first round trip of the look-back
+    // overlaps with those steps and with the scatter.
+    constexpr bool LB_SPLIT = THREADS >= 2 * kRadix;
+    const bool is_lb = LB_SPLIT ? (tid >= (u32)kRadix && tid < 2u * kRadix) : tid < (u32)kRadix;
+    const u32 lb_digit = LB_SPLIT ? tid - kRadix : tid;
+    constexpr int LB = 2;  // predecessor tiles read per round trip
+    u64 lb_w[LB];
+    auto lb_read = [&](long long t) {  // descriptors of tiles t, t-1, ... for my digit
+#pragma unroll
+        for (int k = 0; k < LB; ++k)
+            lb_w[k] = t - k >= 0 ? ld_relaxed_u64(a.desc + (u64)(t - k) * kRadix + lb_digit) : tag_pfx;  // before tile 0: prefix 0
+    };
+    if (LB_SPLIT && is_lb && tile > 0) lb_read((long long)tile - 1);
 
     // ---- 3. per digit: count over the warps, publish the tile aggregate -------------------------
-    u32 cnt = 0;       // keys of digit `tid` in the tile, pads included
-    u32 cnt_real = 0;  // pads excluded (they all have digit 255)
+    u32 cnt = 0;  // keys of digit `tid` in the tile, pads included
     if (tid < kRadix) {
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) cnt += s_whist[w * kRadix + tid];
-        cnt_real = cnt;
+        u32 cnt_real = cnt;  // pads excluded (they all have digit 255)
         if (!full && tid == kRadix - 1) cnt_real = cnt - ((u32)TILE - count);
         st_relaxed_u64(my_desc + tid, (tile == 0 ? tag_pfx : tag_agg) | (u64)cnt_real);
+        s_cnt[tid] = cnt_real;
     }
+    if (!LB_SPLIT && is_lb && tile > 0) lb_read((long long)tile - 1);
     // ---- 4. exclusive scan of the digit counts: start of each digit's run in the sorted tile ----
     u32 incl = cnt;
     if (tid < kRadix) {
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const u32 up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-            if (lane >= (u32)d) incl += up;
+            incl += lane >= (u32)d ? up : 0u;
         }
         if (lane == 31) s_misc[warp] = incl;
     }
     __syncthreads();
-    u32 dexcl = 0;  // exclusive prefix of digit `tid` within the tile
     if (tid < kRadix) {
         u32 wbase = 0;
 #pragma unroll
-        for (int w = 0; w < kRadix / 32; ++w)
-            if (w < (int)warp) wbase += s_misc[w];
-        dexcl = wbase + incl - cnt;
+        for (int w = 0; w < kRadix / 32; ++w) wbase += w < (int)warp ? s_misc[w] : 0u;
+        const u32 dexcl = wbase + incl - cnt;  // exclusive prefix of digit `tid` within the tile
+        s_dexcl[tid] = dexcl;
         // Turn the per-warp counts into the position of each (warp, digit) group in the sorted tile.
         u32 run = dexcl;
 #pragma unroll
@@ -267,6 +332,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
     }
     __syncthreads();
 
+    KF_STRACE(3);
     // ---- 5. scatter keys (and values) to their sorted position in shared memory -----------------
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
@@ -279,7 +345,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         ValS val[ITEMS];
         if (full) {
 #pragma unroll
-            for (int i = 0; i < ITEMS; ++i) val[i] = vin[tile_start + warp_off + i * 32];
+            for (int i = 0; i < ITEMS; ++i) val[i] = (vin + tile_start + warp_off)[i * 32];
         } else {
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
@@ -291,47 +357,63 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         for (int i = 0; i < ITEMS; ++i) s_vals[rank[i]] = val[i];
     }
 
-    // ---- 6. look back: keys of digit `tid` in all earlier tiles ----------------------------------
-    if (tid < kRadix) {
+    KF_STRACE(4);
+    // ---- 6. look back: keys of my digit in all earlier tiles, LB tiles per round trip; the first
+    //         round was read before the scatter ------------------------------------------------------
+    if (is_lb) {
         u64 excl = 0;
         bool ok = true;
         if (tile > 0) {
-            u64 t = tile - 1;
+            long long t = (long long)tile - 1;
             u32 spins = 0;
-            while (true) {
-                const u64 w = ld_relaxed_u64(a.desc + t * kRadix + tid);
-                const u64 tag = w & ~kCountMask;
-                if (tag == tag_pfx) {
-                    excl += w & kCountMask;
-                    break;
-                } else if (tag == tag_agg) {
-                    excl += w & kCountMask;
-                    --t;  // tile 0 always publishes a prefix, so t never passes 0
-                    spins = 0;
-                } else if (tag == tag_poison) {
-                    ok = false;
-                    break;
-                } else {
+            bool done = false;
+            while (!done) {
+                int used = 0;
+#pragma unroll
+                for (int k = 0; k < LB; ++k) {
+                    if (!done && used == k) {
+                        const u64 w = lb_w[k];
+                        const u64 tag = w & ~kCountMask;
+                        if (tag == tag_pfx) {
+                            excl += w & kCountMask;
+                            done = true;
+                        } else if (tag == tag_agg) {
+                            excl += w & kCountMask;
+                            used = k + 1;
+                        } else if (tag == tag_poison) {
+                            ok = false;
+                            done = true;
+                        }
+                    }
+                }
+                if (done) break;
+                t -= used;  // tile 0 always publishes a prefix, so t never passes below -LB
+                if (used == 0) {
                     if (++spins > kSpinLimit) {
                         record_error(a.header, KF_ERR_TIMEOUT, (u32)tile);
                         ok = false;
                         break;
                     }
                     if (spins > 8) __nanosleep(spins > 64 ? 256 : 32);
+                } else {
+                    spins = 0;
                 }
+                lb_read(t);
             }
         }
         if (ok) {
-            if (tile > 0) st_relaxed_u64(my_desc + tid, tag_pfx | (excl + (u64)cnt_real));
+            if (tile > 0) st_relaxed_u64(my_desc + lb_digit, tag_pfx | (excl + (u64)s_cnt[lb_digit]));
             // Global index of element idx of the sorted tile with digit d: gbase[d] + idx.
-            s_gbase[tid] = a.gexcl[tid] + excl - (u64)dexcl;
+            s_gbase[lb_digit] = a.gexcl[lb_digit] + excl - (u64)s_dexcl[lb_digit];
         } else {
-            st_relaxed_u64(my_desc + tid, tag_poison);
+            st_relaxed_u64(my_desc + lb_digit, tag_poison);
             s_misc[10] = 1;
         }
     }
+    KF_STRACE(5);
     __syncthreads();
     if (s_misc[10]) return;
+    KF_STRACE(6);
 
     // ---- 7. stream the sorted tile out: consecutive threads write consecutive addresses within
     //         each digit's run ----------------------------------------------------------------
@@ -346,13 +428,14 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
             if constexpr (SM::HAS_VAL) static_cast<ValS *>(a.vals_out)[o] = s_vals[idx];
         }
     }
+    KF_STRACE(7);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
 struct SortVariant {
     int threads, items;
 };
-static const SortVariant kSortVariants[] = {{256, 16}, {512, 16}, {512, 24}, {1024, 16}};
+static const SortVariant kSortVariants[] = {{256, 16}, {512, 16}, {512, 24}, {384, 24}};
 constexpr int kNumSortVariants = 4;
 
 template <typename KeyT, bool IS_FLOAT, typename ValT, int THREADS, int ITEMS>
@@ -372,7 +455,7 @@ int onesweep_launch(int variant, const SortPassArgs &a, cudaStream_t s) {
     case 0: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 256, 16>(a, s);
     case 1: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 512, 16>(a, s);
     case 2: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 512, 24>(a, s);
-    case 3: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 1024, 16>(a, s);
+    case 3: return onesweep_launch_one<KeyT, IS_FLOAT, ValT, 384, 24>(a, s);
     default: return KF_ERR_UNSUPPORTED;
     }
 }

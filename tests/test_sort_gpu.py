@@ -148,7 +148,7 @@ def test_key_value_errors(kf):
         kf.sort(v.to(torch.int16))
 
 
-@pytest.mark.parametrize("workgroup,nitem", [(256, 16), (512, 16), (512, 24), (1024, 16)])
+@pytest.mark.parametrize("workgroup,nitem", [(256, 16), (512, 16), (512, 24), (384, 24)])
 def test_launch_variants_and_stability(kf, oracle, workgroup, nitem):
     """Every compiled tile shape: same bits as the oracle, stable at every shape, and a tile shape
     outside the compiled set raises while the context stays usable."""
