@@ -38,7 +38,8 @@ typedef enum kf_status {
     KF_ERR_WORKSPACE_TOO_SMALL = 3,
     KF_ERR_LAUNCH_FAILED = 4,      /* a CUDA runtime call failed; see kf_last_cuda_error() */
     KF_ERR_TIMEOUT = 5,            /* a bounded device-side wait ran out (reported by kf_check) */
-    KF_ERR_EMPTY_REDUCTION = 6     /* mapreduce over n == 0 has no value (no init element) */
+    KF_ERR_EMPTY_REDUCTION = 6,    /* mapreduce over n == 0 has no value (no init element) */
+    KF_ERR_EXCEEDS_STATIC_SCRATCH = 7 /* kf_scan_static: the input needs more than KF_SCAN_STATIC_SCRATCH_BYTES */
 } kf_status;
 
 /* Element types: the reference's BitwiseTypes (src/KernelForge.jl:15) without Float16. */
@@ -165,6 +166,33 @@ int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, float *a_dst,
  * scan!(op, dst, src) over a Vector{NTuple{2,Float32}} (src/scan/scan.jl:261-284). */
 int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab,
                            void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
+/* Size of the fixed device array behind kf_scan_static: 1 MiB, held by every GPU that loads the
+ * library until the process exits. It bounds the input: the call is refused when
+ * kf_scan_workspace_bytes(dtype, 0, n, NULL) exceeds it (about 2^30 elements of up to 4 bytes,
+ * 2^28 elements of 8 bytes). */
+#define KF_SCAN_STATIC_SCRATCH_BYTES (1u << 20)
+
+/* kf_scan for callers that cannot hand over a workspace because they cannot allocate device memory
+ * at the point of the call. It has no counterpart in the reference, whose scan! allocates its
+ * descriptors itself when `tmp` is not given (src/scan/scan.jl:291-307). Typical callers: code that
+ * runs under a host framework's memory pool and must not call cudaMalloc behind its back, a process
+ * that sits close to the device's memory limit where an allocation may fail or stall, and
+ * latency-sensitive loops where cudaMalloc / cudaFree would synchronise the device.
+ *
+ * Same arguments, semantics and results as kf_scan with cfg == NULL, minus `ws`, `ws_bytes`, `cfg`.
+ * The tile descriptors live in a fixed 1 MiB device array inside the library; the call itself
+ * calls no cudaMalloc, cudaFree or allocating library routine.
+ *   - The FIRST call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current) and caches it; make that first call before any stream capture.
+ *   - All calls on one device share the array, and it keeps what the last call left there. Each call
+ *     clears the part it uses first, so calls that follow one another on a stream are fine. Calls
+ *     that overlap on the GPU (different streams, no ordering between them) race: do not do that.
+ *   - Inputs whose descriptors do not fit return KF_ERR_EXCEEDS_STATIC_SCRATCH and touch nothing.
+ *   - There is no workspace pointer to hand to kf_check; a device-side timeout shows as an output
+ *     that was not written. */
+int32_t kf_scan_static(int32_t f, int32_t op, int32_t dtype,
+                       const void *src, void *dst, uint64_t n, const void *init, kf_stream_t stream);
 
 /* ---- sort ---------------------------------------------------------------------------------- */
 

@@ -14,7 +14,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libkf_b200.so")
 
 # kf_status
-OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE_TOO_SMALL, ERR_LAUNCH_FAILED, ERR_TIMEOUT, ERR_EMPTY = range(7)
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE_TOO_SMALL, ERR_LAUNCH_FAILED, ERR_TIMEOUT, ERR_EMPTY, \
+    ERR_EXCEEDS_STATIC_SCRATCH = range(8)
 # kf_dtype
 U8, I8, U16, I16, U32, I32, U64, I64, F32, F64 = range(10)
 # kf_map / kf_op / kf_post / kf_primitive
@@ -52,6 +53,7 @@ PROTOTYPES = {
     "kf_scan_workspace_bytes": (c_size_t, [c_int32, c_int32, c_uint64, POINTER(LaunchCfg)]),
     "kf_scan": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_void_p, c_uint64, c_void_p,
                           c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
+    "kf_scan_static": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_void_p, c_uint64, c_void_p, c_void_p]),
     "kf_scan_affine_soa": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_void_p,
                                      c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_scan_affine_aos": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p,
@@ -101,7 +103,7 @@ def check(code: int, what: str) -> None:
     msg = "%s: %s" % (what, error_string(code))
     if code == ERR_LAUNCH_FAILED:
         msg += " [cudaError %d]" % load().kf_last_cuda_error()
-    if code in (ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_EMPTY):
+    if code in (ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_EMPTY, ERR_EXCEEDS_STATIC_SCRATCH):
         raise ArgumentError(msg)
     raise KernelForgeError(msg)
 

@@ -36,6 +36,7 @@ extern "C" const char *kf_error_string(int32_t status) {
     case KF_ERR_LAUNCH_FAILED: return "a CUDA runtime call failed (see kf_last_cuda_error)";
     case KF_ERR_TIMEOUT: return "a bounded device-side wait on a tile descriptor ran out";
     case KF_ERR_EMPTY_REDUCTION: return "reducing over an empty collection is not allowed (no init value)";
+    case KF_ERR_EXCEEDS_STATIC_SCRATCH: return "input too large for kf_scan_static: its tile descriptors exceed KF_SCAN_STATIC_SCRATCH_BYTES; use kf_scan with a workspace";
     default: return "unknown kf_status";
     }
 }

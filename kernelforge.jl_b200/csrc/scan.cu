@@ -2,6 +2,8 @@
 // The kernels live in scan_impl.cuh and are instantiated per element type in scan_inst_*.cu.
 #include "scan_launch.cuh"
 
+#include <mutex>
+
 namespace kf {
 
 int scan_plan(int elem_bytes, int epv, int narr, u64 n, const kf_launch_cfg *cfg, ScanPlan *plan) {
@@ -157,4 +159,48 @@ extern "C" int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     return scan_dispatch_affine_aos(p.variant, ab_src, ab_dst, a, s);
+}
+
+// ---- scan without a caller-supplied workspace ---------------------------------------------------------
+// The tile descriptors and the ticket of kf_scan live in this fixed device array instead of a
+// workspace the caller allocates. Every GPU that loads the library carries the array until the
+// process exits. In host code the array's NAME is only a stand-in; its device address comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char g_scan_static_scratch[KF_SCAN_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void *g_static_ptr[kMaxDevices] = {};
+
+// Device address of the static scratch on the current device (set-up on first use per device).
+int static_scratch(void **out) {
+    int dev = 0;
+    KF_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return KF_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void *ptr = nullptr;
+        KF_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_scan_static_scratch));
+        if (!ptr) return KF_ERR_LAUNCH_FAILED;
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return KF_OK;
+}
+}  // namespace
+
+extern "C" int32_t kf_scan_static(int32_t f, int32_t op, int32_t dtype, const void *src, void *dst, uint64_t n,
+                                  const void *init, kf_stream_t stream) {
+    // Size first: a request beyond the fixed scratch is refused before anything touches the device.
+    const size_t need = kf_scan_workspace_bytes(dtype, 0, n, nullptr);
+    if (need == 0 && n != 0) return dtype_bytes(dtype) ? KF_ERR_UNSUPPORTED : KF_ERR_INVALID_ARG;
+    if (need > (size_t)KF_SCAN_STATIC_SCRATCH_BYTES) return KF_ERR_EXCEEDS_STATIC_SCRATCH;
+    if (n == 0) return KF_OK;
+    void *ws = nullptr;
+    const int rc = static_scratch(&ws);
+    if (rc != KF_OK) return rc;
+    // kf_scan clears the header and the descriptors it is going to use at the start of the call, so
+    // whatever the previous call left in the array does no harm.
+    return kf_scan(f, op, dtype, src, dst, n, init, ws, (size_t)KF_SCAN_STATIC_SCRATCH_BYTES, nullptr, stream);
 }

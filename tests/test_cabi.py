@@ -30,7 +30,9 @@ def test_header_symbols_are_exported_and_bound(kf):
 def test_header_cites_reference_for_every_entry(kf):
     text = open(HEADER).read()
     for name in declared_symbols():
-        i = text.rindex(name + "(")  # the declaration, not a mention in an earlier comment
+        m = re.search(r"^(?:int32_t|size_t|const char \*)\s*" + name + r"\(", text, flags=re.M)  # the declaration itself
+        assert m, name
+        i = m.start()
         comment = text[text.rfind("/*", 0, i):i]
         assert re.search(r"\.jl:\d+|no counterpart|ABI version|last KF_ERR|SMs of the current", comment), name
 
