@@ -239,6 +239,54 @@ def primitives_table(kf, torch, peak, iters=10):
     return out
 
 
+def run_case(args):
+    """One primitive, `--steps` calls at n = 2^log2n on cuda:0, timed with CUDA events. Meant to be run
+    under a profiler on a small case (inputs larger than L2, a few hundred MB on the device)."""
+    import torch
+    from __graft_entry__ import load_package
+    kf = load_package()
+    torch.cuda.set_device(0)
+    n = 1 << args.log2n
+    g = torch.Generator(device="cuda").manual_seed(0)
+    case = args.case
+    if case in ("scan_u32", "scan_f32", "mapreduce_f32"):
+        x = (torch.randint(0, 256, (n,), dtype=torch.int32, device="cuda", generator=g).view(torch.uint32)
+             if case == "scan_u32" else torch.rand(n, dtype=torch.float32, device="cuda", generator=g))
+        if case == "mapreduce_f32":
+            dst = torch.empty(1, dtype=torch.float32, device="cuda")
+            tmp = kf.get_allocation(kf.MapReduce1D, kf.identity, "+", x)
+            fn, nbytes = (lambda: kf.mapreduce_(kf.identity, "+", dst, x, tmp=tmp)), 4 * n
+        else:
+            dst = torch.empty_like(x)
+            tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", x)
+            fn, nbytes = (lambda: kf.scan_("+", dst, x, tmp=tmp)), 8 * n
+    elif case == "scan_affine":
+        a = 0.5 + 0.5 * torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+        b = 2.0 * torch.rand(n, dtype=torch.float32, device="cuda", generator=g) - 1.0
+        da, db = torch.empty_like(a), torch.empty_like(b)
+        tmp = kf.get_allocation(kf.Scan1D, kf.identity, kf.AffineCompose(), (a, b))
+        fn, nbytes = (lambda: kf.scan_(kf.AffineCompose(), (da, db), (a, b), tmp=tmp)), 16 * n
+    elif case in ("sort_u32", "sort_f32", "sort_pairs"):
+        keys = (torch.randn(n, dtype=torch.float32, device="cuda", generator=g) if case == "sort_f32" else
+                torch.randint(0, 1 << 32, (n,), dtype=torch.int64, device="cuda", generator=g).to(torch.int32).view(torch.uint32))
+        out = torch.empty_like(keys)
+        if case == "sort_pairs":
+            idx = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
+            vout = torch.empty_like(idx)
+            tmp = kf.get_allocation(kf.Sort1D, idx, keys=keys)
+            fn, nbytes = (lambda: kf.sort_(vout, idx, keys=keys, keys_dst=out, tmp=tmp)), 68 * n
+        else:
+            tmp = kf.get_allocation(kf.Sort1D, keys)
+            fn, nbytes = (lambda: kf.sort_(out, keys, tmp=tmp)), 36 * n
+    else:
+        raise SystemExit("unknown --case %r" % case)
+    fn()
+    ms = time_gpu(fn, max(1, args.steps), torch)
+    rc = kf.lib.kf_check(tmp.ptr(), None)
+    print(json.dumps({"case": case, "n": n, "ms": round(ms, 4), "GB/s": round(nbytes / ms / 1e6, 1), "device_status": rc}))
+    return 0 if rc == 0 else 1
+
+
 def run_gpu_arm(args):
     import numpy as np
     import torch
@@ -317,10 +365,10 @@ def run_gpu_arm(args):
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         with open(tpath) as fh:
-            traffic = json.load(fh).get("scan_kernel_u32_2p28_bytes_per_launch")
+            traffic = json.load(fh).get("scan_kernel_ring_u32_2p28_bytes_per_launch")
     except Exception:
         pass
-    roofline = {"bound": "hbm", "kernel": "scan_kernel<uint32, +, 512x4>", "achieved": round(achieved, 1),
+    roofline = {"bound": "hbm", "kernel": "scan_kernel_ring<uint32, +, 768x4, 4 buffers, 2 tiles ahead>", "achieved": round(achieved, 1),
                 "peak": peak, "peak_kind": peak_kind + " (STREAM-style copy)", "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                 "algorithmic_bytes_per_launch": 8 * n, "kernel_ms": round(kern_ms, 4), "traffic": traffic}
@@ -400,7 +448,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--detail", type=int, default=1, help="1: also measure the other primitives (single GPU)")
+    ap.add_argument("--case", default=None,
+                    help="run ONE primitive a few times at n=2^log2n and exit (small case for profiler captures): "
+                         "scan_u32, scan_f32, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_pairs")
+    ap.add_argument("--log2n", type=int, default=26)
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.impl == "reference":
         return run_reference_arm(args)
     return run_gpu_arm(args)
