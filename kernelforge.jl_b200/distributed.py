@@ -71,8 +71,9 @@ class LocalOps:
         return out
 
     def take(self, x, positions):
-        """x[positions] for a small index tensor (sample extraction)."""
-        return x[positions]
+        """x[positions] for a small index tensor (sample extraction). torch cannot index unsigned
+        16/32/64-bit tensors, so the gather runs on the signed twin of the same bits."""
+        return _bits_view(x)[positions].view(x.dtype)
 
 
 _DEFAULT_OPS = LocalOps()
@@ -144,7 +145,7 @@ def choose_splitters(sorted_samples, world: int):
     """world-1 splitters from the globally sorted samples: every world-th quantile."""
     per = sorted_samples.numel() // world
     pos = torch.arange(1, world, device=sorted_samples.device) * per
-    return sorted_samples[pos]
+    return _bits_view(sorted_samples)[pos].view(sorted_samples.dtype)
 
 
 def sort(group: ShardGroup, x, *, local: LocalOps = _DEFAULT_OPS, samples_per_rank: int = SAMPLES_PER_RANK):
