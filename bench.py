@@ -287,6 +287,121 @@ def run_case(args):
     return 0 if rc == 0 else 1
 
 
+def run_sharded(args):
+    """Global n = 2^global_log2n split into equal contiguous shards: mapreduce(+) over Float32 U[0,1),
+    inclusive scan over UInt32 U{0..255}, sample sort of uniform UInt32 keys (1024 samples per GPU,
+    NCCL all-to-all). Device-timed, max over ranks; results are verified with size-independent checks."""
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    kf = load_package()
+    from kernelforge_jl_b200 import distributed as kfd
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", local))
+    peak, _ = measured_peak()
+    n = 1 << args.global_log2n
+    n_per = n // world
+    g = torch.Generator(device="cuda").manual_seed(7000 + rank)
+    group = kfd.ShardGroup()
+
+    def fill_u32(full_range):
+        out = torch.empty(n_per, dtype=torch.int32, device="cuda")
+        step = 1 << 26
+        for lo in range(0, n_per, step):
+            hi = min(n_per, lo + step)
+            hi_val = (1 << 32) if full_range else 256
+            out[lo:hi] = torch.randint(0, hi_val, (hi - lo,), dtype=torch.int64, device="cuda", generator=g).to(torch.int32)
+        return out.view(torch.uint32)
+
+    def timed(fn, iters):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    res = {}
+    xf = torch.rand(n_per, dtype=torch.float32, device="cuda", generator=g)
+    ms = timed(lambda: kfd.mapreduce(group, kf.identity, "+", xf, to_cpu=False), args.steps)
+    got = kfd.mapreduce(group, kf.identity, "+", xf)
+    ref = xf.sum(dtype=torch.float64)
+    dist.all_reduce(ref)
+    assert abs(got - ref.item()) <= 1e-5 * args.global_log2n * ref.item(), (got, ref.item())
+    res["mapreduce_f32"] = (4 * n, ms)
+    del xf
+
+    xu = fill_u32(False)
+    du = torch.empty_like(xu)
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", xu)
+    ms = timed(lambda: kfd.scan_(group, "+", du, xu, tmp=tmp), args.steps)
+    d32, x32 = du.view(torch.int32), xu.view(torch.int32)
+    assert bool(((d32[1:] - d32[:-1]) == x32[1:]).all().item())
+    tot = x32.sum(dtype=torch.int64).reshape(1)
+    tots = [torch.zeros_like(tot) for _ in range(world)]
+    dist.all_gather(tots, tot)
+    expect_last = int(sum(int(t.item()) for t in tots[: rank + 1])) & 0xFFFFFFFF
+    assert (int(d32[-1].item()) & 0xFFFFFFFF) == expect_last
+    res["scan_u32"] = (8 * n, ms)
+    del xu, du, tmp, d32, x32
+
+    keys = fill_u32(True)
+    k64 = keys.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    chk = torch.stack([k64.sum(), (k64 * k64 + 7 * k64).sum()])
+    del k64
+    dist.all_reduce(chk)
+    out_holder = {}
+
+    def do_sort():
+        out_holder["r"] = kfd.sort(group, keys)
+    ms = timed(do_sort, max(1, args.steps // 2))
+    chunk, counts = out_holder["r"]
+    assert sum(counts) == n
+    c64 = chunk.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    assert bool((c64[1:] >= c64[:-1]).all().item())
+    chk2 = torch.stack([c64.sum(), (c64 * c64 + 7 * c64).sum()])
+    dist.all_reduce(chk2)
+    assert torch.equal(chk, chk2)
+    edge = torch.stack([c64[0], c64[-1]])
+    edges = [torch.zeros_like(edge) for _ in range(world)]
+    dist.all_gather(edges, edge)
+    for r in range(1, world):
+        assert int(edges[r][0].item()) >= int(edges[r - 1][1].item())
+    res["sample_sort_u32"] = (36 * n, ms)
+    imbalance = max(counts) / (n / world)
+
+    if rank == 0:
+        line = {"metric": "effective GB/s (single-device algorithmic bytes on the global n / max device time over ranks)",
+                "n_gpus": world, "scaling": "strong", "data": "synthetic", "global_n": n, "steps": args.steps,
+                "config": {"workload": "sharded: mapreduce(+) Float32, inclusive scan UInt32, sample sort UInt32 keys; "
+                                       "global n=2^%d in %d contiguous shards" % (args.global_log2n, world),
+                           "sort_max_piece_over_mean": round(imbalance, 4)},
+                "results": {k: {"ms": round(ms_, 4), "GB/s": round(b / ms_ / 1e6, 1),
+                                "frac_of_measured_peak_x_gpus": round(b / ms_ / 1e6 / (peak * world), 4),
+                                "frac_of_nominal_8TBs_x_gpus": round(b / ms_ / 1e6 / (NOMINAL_HBM_GBS * world), 4)}
+                            for k, (b, ms_) in res.items()}}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
 def run_gpu_arm(args):
     import numpy as np
     import torch
@@ -452,9 +567,15 @@ def main():
                     help="run ONE primitive a few times at n=2^log2n and exit (small case for profiler captures): "
                          "scan_u32, scan_f32, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_pairs")
     ap.add_argument("--log2n", type=int, default=26)
+    ap.add_argument("--sharded", action="store_true",
+                    help="measure the sharded configuration instead (mapreduce, scan and sample sort over one global "
+                         "array of 2^--global-log2n elements split across the ranks; strong scaling)")
+    ap.add_argument("--global-log2n", type=int, default=32)
     args = ap.parse_args()
     if args.case:
         return run_case(args)
+    if args.sharded:
+        return run_sharded(args)
     if args.impl == "reference":
         return run_reference_arm(args)
     return run_gpu_arm(args)

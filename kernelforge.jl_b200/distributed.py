@@ -119,6 +119,8 @@ def scan_(group: ShardGroup, *args, tmp=None, local: LocalOps = _DEFAULT_OPS):
     else:
         f, op, dst, src = args
     affine = isinstance(op, ops.AffineCompose)
+    if group.world == 1:
+        return local.scan_(f, op, dst, src, tmp=tmp)  # a single shard needs no carry
     if affine:
         # ordered route: the shard total is the last element of a local scan
         local.scan_(f, op, dst, src, tmp=tmp)
