@@ -480,10 +480,10 @@ def run_gpu_arm(args):
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         with open(tpath) as fh:
-            traffic = json.load(fh).get("scan_kernel_ring_u32_2p28_bytes_per_launch")
+            traffic = json.load(fh).get("scan_kernel_roles_u32_2p28_bytes_per_launch")
     except Exception:
         pass
-    roofline = {"bound": "hbm", "kernel": "scan_kernel_ring<uint32, +, 768x4, 4 buffers, 2 tiles ahead>", "achieved": round(achieved, 1),
+    roofline = {"bound": "hbm", "kernel": "scan_kernel_roles<uint32, +, 768x4, 2 buffers, reduction 3 tiles ahead>", "achieved": round(achieved, 1),
                 "peak": peak, "peak_kind": peak_kind + " (STREAM-style copy)", "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                 "algorithmic_bytes_per_launch": 8 * n, "kernel_ms": round(kern_ms, 4), "traffic": traffic}

@@ -3,21 +3,22 @@
 // scan_inst_*.cu instantiates.
 #pragma once
 
-#include "scan_tma.cuh"
+#include "scan_roles.cuh"
 
 namespace kf {
 
-// `vecs` is 16-byte vectors per thread per tile and per array. Ring variants stage tiles through
-// shared memory with the bulk-copy engine and need 16-byte aligned arrays; the direct variants
-// work on anything and serve as their fallback (and as the small-input path).
+// `vecs` is 16-byte vectors per thread per tile and per array. The persistent (`ring`) variants
+// read tiles ahead through shared memory with the bulk-copy engine and need 16-byte aligned
+// arrays; the direct variants work on anything and serve as their fallback (and as the
+// small-input path).
 struct ScanVariant {
     int threads, vecs;
     bool ring;
 };
 static const ScanVariant kScanVariants[] = {
     {256, 4, false}, {512, 4, false}, {256, 8, false}, {128, 8, false},  // direct
-    {768, 4, true},                                                      // ring: 4 buffers, 2 tiles scanned ahead
-    {992, 4, true},                                                      // ring: 3 buffers, 1 tile scanned ahead
+    {768, 4, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead
+    {640, 4, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead
 };
 constexpr int kNumScanVariants = 6;
 constexpr int kScanFallbackVariant = 1;  // direct 512x4: what a ring variant falls back to
@@ -39,18 +40,18 @@ inline u64 scan_tile_elems(int variant, int epv, int narr) {
 
 int scan_plan(int elem_bytes, int epv, int narr, u64 n, const kf_launch_cfg *cfg, ScanPlan *plan);
 
-template <typename T, typename Op, typename Access, typename Arrays, int THREADS, int VECS, int NBUF, int AHEAD>
+template <typename T, typename Op, typename Access, typename Arrays, int THREADS, int VECS, int NBUF, int K, int LAG>
 int scan_launch_ring_one(const Access &acc, const Arrays &arr, const ScanArgs &args, cudaStream_t s) {
-    using SM = ScanRingSmem<Arrays, T, THREADS, VECS, NBUF, AHEAD>;
+    constexpr int DEPTH = 8, NRES = 1;  // one resolver warp, 256 descriptors per round trip
+    using SM = ScanRolesSmem<Arrays, T, THREADS, VECS, NBUF, K>;
     static_assert(SM::kBytes <= 227 * 1024, "ring does not fit in shared memory");
-    auto kern = scan_kernel_ring<T, Op, Access, Arrays, THREADS, VECS, NBUF, AHEAD, false>;
+    constexpr int CTA = THREADS + 32 + 32 * NRES;
+    auto kern = scan_kernel_roles<T, Op, Access, Arrays, THREADS, VECS, NBUF, K, DEPTH, NRES, LAG>;
     KF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes));
-    int per_sm = 0;
-    KF_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS + 32, SM::kBytes));
-    if (per_sm < 1) return KF_ERR_LAUNCH_FAILED;
-    u64 grid = (u64)device_sm_count() * per_sm;
+    // One CTA per SM: the look-ahead distance K is tuned for tiles of that size arriving at that rate.
+    u64 grid = (u64)device_sm_count();
     if (grid > args.ntiles) grid = args.ntiles;
-    kern<<<(unsigned)grid, THREADS + 32, SM::kBytes, s>>>(acc, arr, args);
+    kern<<<(unsigned)grid, CTA, SM::kBytes, s>>>(acc, arr, args);
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }
@@ -64,8 +65,8 @@ int scan_launch(int variant, const Access &acc, const Arrays &arr, const ScanArg
     case 1: scan_kernel<T, Op, Access, 512, 4><<<grid, 512, 0, s>>>(acc, args); break;
     case 2: scan_kernel<T, Op, Access, 256, 8><<<grid, 256, 0, s>>>(acc, args); break;
     case 3: scan_kernel<T, Op, Access, 128, 8><<<grid, 128, 0, s>>>(acc, args); break;
-    case 4: return scan_launch_ring_one<T, Op, Access, Arrays, 768, RV, 4, 2>(acc, arr, args, s);
-    case 5: return scan_launch_ring_one<T, Op, Access, Arrays, 992, RV, 3, 1>(acc, arr, args, s);
+    case 4: return scan_launch_ring_one<T, Op, Access, Arrays, 768, RV, 2, 3, 2>(acc, arr, args, s);
+    case 5: return scan_launch_ring_one<T, Op, Access, Arrays, 640, RV, 2, 3, 1>(acc, arr, args, s);
     default: return KF_ERR_UNSUPPORTED;
     }
     KF_CUDA_TRY(cudaGetLastError());
