@@ -16,7 +16,7 @@ static const LaunchRow kLaunchTable[] = {
     {0, 0, 1048576ull, 256, 4, 1},
     {0, 0, 16777216ull, 256, 4, 4},
     {0, 0, 18446744073709551615ull, 512, 4, 4},
-    {1, 0, 16777216ull, 256, 8, 0},
+    {1, 0, 4194304ull, 256, 8, 0},
     {1, 0, 18446744073709551615ull, 768, 4, 0},
     {2, 4, 18446744073709551615ull, 512, 24, 0},
     {2, 0, 18446744073709551615ull, 512, 16, 0},
