@@ -497,11 +497,11 @@ def run_gpu_arm(args):
         hu.copy_(xu.view(torch.int32))
         of = torch.empty(n, dtype=torch.float32).pin_memory()
         ou = torch.empty(n, dtype=torch.int32).pin_memory()
-        pipe = kfd.HostScanPipeline(kf, n, chunks=8)
+        pipe = kfd.HostScanPipeline(kf, n, chunk_bytes=args.e2e_chunk_mb << 20, slots=4)
 
         def e2e_step():
-            pipe.scan_host("+", of, hf)
-            pipe.scan_host("+", ou.view(torch.uint32) if hasattr(torch, "uint32") else ou, hu.view(torch.uint32))
+            pipe.scan_host_many([("+", of, hf),
+                                 ("+", ou.view(torch.uint32) if hasattr(torch, "uint32") else ou, hu.view(torch.uint32))])
 
         for _ in range(2):
             e2e_step()
@@ -524,7 +524,7 @@ def run_gpu_arm(args):
             raise SystemExit("bench: host-pipeline scan output failed its difference check")
         e2e = {"value": round(world * 2 * 8 * n / (e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                "h2d_bytes_per_step": 2 * 4 * n, "d2h_bytes_per_step": 2 * 4 * n, "ms_per_step": round(e_ms, 3),
-               "note": "independent per-rank host arrays; chunked H2D / scan(init=carry) / D2H pipeline"}
+               "note": "independent per-rank host arrays; %d MiB chunks through a 4-slot device ring: H2D / scan(init=carry) / D2H on three streams" % args.e2e_chunk_mb}
         del hf, hu, of, ou, pipe
 
     line = None
@@ -571,6 +571,7 @@ def main():
                     help="measure the sharded configuration instead (mapreduce, scan and sample sort over one global "
                          "array of 2^--global-log2n elements split across the ranks; strong scaling)")
     ap.add_argument("--global-log2n", type=int, default=32)
+    ap.add_argument("--e2e-chunk-mb", type=int, default=32, help="chunk size of the host-buffer pipeline (MiB)")
     args = ap.parse_args()
     if args.case:
         return run_case(args)

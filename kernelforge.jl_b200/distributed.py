@@ -186,53 +186,78 @@ def sort(group: ShardGroup, x, *, local: LocalOps = _DEFAULT_OPS, samples_per_ra
 class HostScanPipeline:
     """`scan!` for arrays that live in pinned HOST memory.
 
-    The input is cut into chunks; chunk c is copied in on one stream, scanned on a second stream
-    with `init` = the last output element of chunk c-1 (still on the device), and copied out on a
-    third, so the two PCIe directions and the kernel overlap. Device staging buffers and the scan
-    workspace are allocated once.
+    The arrays are cut into chunks that flow through a small ring of device staging slots: chunk c is
+    copied in on one stream, scanned on a second stream with `init` = the last output element of
+    chunk c-1 (still in its slot), and copied out on a third, so both PCIe directions and the kernel
+    overlap. Several arrays given to `scan_host_many` form ONE stream of chunks (the carry restarts
+    at every array), so the pipeline fills and drains once per call, not once per array. Device
+    memory: 2 * slots * chunk_bytes, whatever the array sizes; slots are guarded by events.
     """
 
-    def __init__(self, kf_module, max_n: int, chunks: int = 8, device=None):
+    def __init__(self, kf_module, max_n: int, chunks: int = 0, device=None, chunk_bytes: int = 32 << 20, slots: int = 4):
         self.kf = kf_module
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.max_n = max_n
-        self.chunks = chunks
-        self.stage_in = torch.empty(max_n * 8, dtype=torch.uint8, device=self.device)
-        self.stage_out = torch.empty(max_n * 8, dtype=torch.uint8, device=self.device)
+        if chunks:  # sized by a chunk count for the largest array (8-byte elements), as earlier versions were
+            chunk_bytes = max(1 << 20, -(-(max_n * 8) // chunks))
+        self.chunk_bytes = (chunk_bytes + 255) // 256 * 256
+        self.slots = max(2, slots)
+        self.stage_in = [torch.empty(self.chunk_bytes, dtype=torch.uint8, device=self.device) for _ in range(self.slots)]
+        self.stage_out = [torch.empty(self.chunk_bytes, dtype=torch.uint8, device=self.device) for _ in range(self.slots)]
+        self.in_free = [None] * self.slots   # event: the scan has read stage_in[k]
+        self.out_free = [None] * self.slots  # event: the copy-out has read stage_out[k]
         self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+        self.counter = 0
         self._tmp = {}
 
     def scan_host(self, op, dst_host, src_host, f=ops.identity):
-        n = src_host.numel()
-        if n > self.max_n or src_host.element_size() > 8:
-            raise C.ArgumentError("HostScanPipeline was sized for %d elements of at most 8 bytes" % self.max_n)
-        if dst_host.numel() != n or dst_host.dtype != src_host.dtype:
-            raise C.ArgumentError("dst and src must match in length and element type")
-        dt = src_host.dtype
-        es = src_host.element_size()
-        d_in = self.stage_in[: n * es].view(dt)
-        d_out = self.stage_out[: n * es].view(dt)
-        per = -(-n // self.chunks)
-        key = (dt, per)
-        if key not in self._tmp:
-            self._tmp[key] = get_allocation(Scan1D, f, op, d_in[:per])
-        tmp = self._tmp[key]
+        return self.scan_host_many([(op, dst_host, src_host, f)])[0]
+
+    def scan_host_many(self, jobs):
+        """jobs: (op, dst_host, src_host[, f]) tuples, scanned independently, pipelined as one stream."""
         cur = torch.cuda.current_stream(self.device)
-        self.s_in.wait_stream(cur)
-        self.s_out.wait_stream(cur)
-        self.s_cmp.wait_stream(cur)
-        lo = 0
-        while lo < n:
-            hi = min(n, lo + per)
-            with torch.cuda.stream(self.s_in):
-                d_in[lo:hi].copy_(src_host[lo:hi], non_blocking=True)
-            self.s_cmp.wait_stream(self.s_in)
-            with torch.cuda.stream(self.s_cmp):
-                init = d_out[lo - 1: lo] if lo > 0 else None
-                _scan_(f, op, d_out[lo:hi], d_in[lo:hi], init=init, tmp=tmp)
-            self.s_out.wait_stream(self.s_cmp)
-            with torch.cuda.stream(self.s_out):
-                dst_host[lo:hi].copy_(d_out[lo:hi], non_blocking=True)
-            lo = hi
+        for st in (self.s_in, self.s_cmp, self.s_out):
+            st.wait_stream(cur)
+        outs = []
+        for job in jobs:
+            op, dst_host, src_host = job[0], job[1], job[2]
+            f = job[3] if len(job) > 3 else ops.identity
+            n = src_host.numel()
+            if n > self.max_n or src_host.element_size() > 8:
+                raise C.ArgumentError("HostScanPipeline was sized for %d elements of at most 8 bytes" % self.max_n)
+            if dst_host.numel() != n or dst_host.dtype != src_host.dtype:
+                raise C.ArgumentError("dst and src must match in length and element type")
+            dt, es = src_host.dtype, src_host.element_size()
+            per = self.chunk_bytes // es
+            carry = None
+            lo = 0
+            while lo < n:
+                hi = min(n, lo + per)
+                k = self.counter % self.slots
+                self.counter += 1
+                d_in = self.stage_in[k][: (hi - lo) * es].view(dt)
+                d_out = self.stage_out[k][: (hi - lo) * es].view(dt)
+                key = (dt, hi - lo)
+                if key not in self._tmp:
+                    self._tmp[key] = get_allocation(Scan1D, f, op, d_in)
+                with torch.cuda.stream(self.s_in):
+                    if self.in_free[k] is not None:
+                        self.s_in.wait_event(self.in_free[k])
+                    d_in.copy_(src_host[lo:hi], non_blocking=True)
+                    arrived = self.s_in.record_event()
+                with torch.cuda.stream(self.s_cmp):
+                    self.s_cmp.wait_event(arrived)
+                    if self.out_free[k] is not None:
+                        self.s_cmp.wait_event(self.out_free[k])
+                    _scan_(f, op, d_out, d_in, init=carry, tmp=self._tmp[key])
+                    scanned = self.s_cmp.record_event()
+                self.in_free[k] = scanned
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(scanned)
+                    dst_host[lo:hi].copy_(d_out, non_blocking=True)
+                    self.out_free[k] = self.s_out.record_event()
+                carry = d_out[hi - lo - 1: hi - lo]  # read by the next chunk's scan, long before the slot is reused
+                lo = hi
+            outs.append(dst_host)
         cur.wait_stream(self.s_out)
-        return dst_host
+        return outs

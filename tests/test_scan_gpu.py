@@ -270,3 +270,30 @@ def test_full_size_2p26_affine(kf):
     refA = np.cumprod(a_h)
     got = da[:2000].double().cpu().numpy()
     assert (np.abs(got - refA) <= tol * np.maximum(refA, 4 * float(np.finfo(np.float32).tiny))).all()
+
+
+def test_host_pipeline_chunk_ring(kf, oracle):
+    """Pinned host arrays through the chunked H2D / seeded scan / D2H ring: several arrays in one
+    call, ragged chunk counts, more chunks than staging slots, the carry restarting at each array."""
+    from kernelforge_jl_b200 import distributed as kfd
+
+    n1, n2 = 1_000_003, 300_001
+    rng = np.random.default_rng(7)
+    a = rng.integers(0, 256, n1).astype(np.uint32)
+    b = rng.integers(-1000, 1000, n2).astype(np.int64)
+    ha = torch.from_numpy(a.view(np.int32)).pin_memory().view(torch.uint32)
+    hb = torch.from_numpy(b).pin_memory()
+    oa = torch.empty(n1, dtype=torch.int32).pin_memory().view(torch.uint32)
+    ob = torch.empty(n2, dtype=torch.int64).pin_memory()
+    pipe = kfd.HostScanPipeline(kf, max(n1, n2), chunk_bytes=1 << 18, slots=3)  # 16 and 10 chunks
+    for _ in range(2):  # a second call reuses slots whose events are still recorded
+        pipe.scan_host_many([("+", oa, ha), ("+", ob, hb)])
+        torch.cuda.synchronize()
+        assert (oa.view(torch.int32).numpy().view(np.uint32) == oracle.c_scan(0, 0, a)).all()
+        assert (ob.numpy() == oracle.c_scan(0, 0, b)).all()
+    c = rng.random(70_000).astype(np.float32)
+    hc = torch.from_numpy(c).pin_memory()
+    oc = torch.empty_like(hc).pin_memory()
+    pipe.scan_host("max", oc, hc)
+    torch.cuda.synchronize()
+    assert (oc.numpy().astype(np.float64) == oracle.c_scan(0, 3, c)).all()
