@@ -198,6 +198,12 @@ def primitives_table(kf, torch, peak, iters=10):
     for _ in range(3):
         fn()
     add("mapreduce_f32_abs2_2p20", 4 << 20, time_gpu(fn, 200, torch), 1)
+    yf = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+    fn = lambda: kf.mapreduce_(kf.prod, "+", dst1, (xf, yf), tmp=tmp)
+    for _ in range(3):
+        fn()
+    add("mapreduce_dot_f32_2p28", 8 * n, time_gpu(fn, iters * 2, torch), 1)
+    del yf
 
     na = 1 << 26
     a = 0.5 + 0.5 * torch.rand(na, dtype=torch.float32, device="cuda", generator=g)
@@ -229,6 +235,14 @@ def primitives_table(kf, torch, peak, iters=10):
         sort_once(kfl, tmps)
     add("sort_f32_keys_2p28", 36 * n, time_gpu(lambda: sort_once(kfl, tmps), iters, torch), 6)
     del kfl, tmps
+    k16 = torch.randint(-32768, 32768, (n,), dtype=torch.int16, device="cuda", generator=g)
+    w16 = torch.empty_like(k16)
+    tmp16 = kf.get_allocation(kf.Sort1D, k16)
+    f16 = lambda: kf.sort_(w16, k16, tmp=tmp16)
+    for _ in range(2):
+        f16()
+    add("sort_i16_keys_2p28", (2 * 2 + 1) * 2 * n, time_gpu(f16, iters, torch), 4)
+    del k16, w16, tmp16
     idx = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
     vout = torch.empty_like(idx)
     tmpp = kf.get_allocation(kf.Sort1D, idx, keys=keys)

@@ -55,6 +55,14 @@ typedef enum kf_map {
     KF_MAP_ABS = 2
 } kf_map;
 
+/* Maps over several arrays at once (the tuple form mapreduce(f, op, (x, y, ...))): what the
+ * reference's tests pass as closures (test/tests/mapreduce/mapreduce1d_test.jl:106-194). */
+typedef enum kf_mapn {
+    KF_MAPN_PROD = 0,              /* x1*x2*...*xk   (k = 2: dot product)        k in 2..4 */
+    KF_MAPN_SQDIFF = 1,            /* (x1 - x2)^2    (squared distance)          k = 2 */
+    KF_MAPN_WSQ = 2                /* x1 * x2 * x2   (weighted sum of squares)   k = 2 */
+} kf_mapn;
+
 /* Binary operator `op`. KF_OP_AFFINE is the non-commutative composition of affine maps
  * (a1,b1) o (a2,b2) = (a1*a2, a2*b1 + b2), i.e. "apply the left map, then the right one". */
 typedef enum kf_op {
@@ -136,6 +144,17 @@ int32_t kf_mapreduce(int32_t f, int32_t op, int32_t g, int32_t dtype,
                      const void *src, uint64_t n, void *dst,
                      void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 
+/* Tuple form: dst[0] = g(op-reduce_i fn(srcs[0][i], ..., srcs[nsrc-1][i])). `srcs` is a HOST array of
+ * `nsrc` device pointers (2..4 arrays of `dtype`, n elements each). Same kernel structure, workspace
+ * (kf_mapreduce_workspace_bytes) and determinism as kf_mapreduce; `op` is one of ADD, MUL, MIN, MAX.
+ * Algorithmic bytes: nsrc * n * sizeof(T). Arrays that do not share their 16-byte misalignment are
+ * read element-wise.
+ * Replaces the tuple methods of mapreduce1d / mapreduce1d! (src/mapreduce/1D/mapreduce1d.jl:177-288,
+ * exercised by test/tests/mapreduce/mapreduce1d_test.jl:106-194). */
+int32_t kf_mapreduce_multi(int32_t fn, int32_t op, int32_t g, int32_t dtype,
+                           const void *const *srcs, int32_t nsrc, uint64_t n, void *dst,
+                           void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
 /* ---- scan ---------------------------------------------------------------------------------- */
 
 /* Workspace for kf_scan / kf_scan_affine_*. Replaces get_allocation(Scan1D, ...)
@@ -201,14 +220,17 @@ int32_t kf_scan_static(int32_t f, int32_t op, int32_t dtype,
  * descriptors, tile tickets and the n-element ping-pong scratch (keys, and values if any). */
 size_t kf_sort_workspace_bytes(int32_t key_dtype, int32_t val_bytes, uint64_t n, const kf_launch_cfg *cfg);
 
-/* Stable ascending LSD radix sort, 8-bit digits, one onesweep pass per key byte. Keys are
+/* Stable ascending LSD radix sort, 8-bit digits, one onesweep pass per key byte (every kf_dtype is
+ * a valid key type: 1, 2, 4 or 8 passes). Keys are
  * ordered by the reference's uint_map (src/sort/uint_map.jl:11-35): unsigned = identity,
  * signed = sign bit flipped, floats = sign-flip / complement (-0.0 before +0.0, NaNs by bit
  * pattern); the original key bits are what is moved. `dst == src` sorts in place.
  * Replaces _sort1d_impl! (src/sort/sort1d.jl:780-874), _sort_histograms! (:655-697),
  * bucket_histogram_kernel! (src/sort/bucket_histogram_kernel.jl:77-145),
  * scan_histogram_kernel! (src/sort/scan_histogram_kernel.jl:20-46) and the onesweep pass
- * kernel (src/sort/onesweep_kernel.jl:113-488). n == 0 is a no-op. */
+ * kernel (src/sort/onesweep_kernel.jl:113-488); one-byte keys take the same kernel with a single
+ * pass instead of the reference's byte_sort_kernel (src/sort/byte_sort_kernel.jl:32-167), which is
+ * not stable across blocks. n == 0 is a no-op. */
 int32_t kf_sort_keys(int32_t key_dtype, const void *src, void *dst, uint64_t n,
                      void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 

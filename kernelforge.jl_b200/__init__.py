@@ -11,7 +11,7 @@ from . import _cabi
 from ._cabi import ArgumentError, KernelForgeError
 from .allocations import KernelBuffer, MapReduce1D, Scan1D, Sort1D, get_allocation
 from .mapreduce import mapreduce, mapreduce_, mapreduce1d, mapreduce1d_
-from .ops import AffineCompose, abs2, identity, sqrt
+from .ops import AffineCompose, abs2, identity, prod, sqdiff, sqrt, wsq
 from .scan import scan, scan_
 from .sort import sort, sort_, sortperm
 
@@ -20,5 +20,5 @@ lib = _cabi.load()
 __all__ = [
     "ArgumentError", "KernelForgeError", "KernelBuffer", "MapReduce1D", "Scan1D", "Sort1D", "get_allocation",
     "mapreduce", "mapreduce_", "mapreduce1d", "mapreduce1d_", "scan", "scan_", "sort", "sort_", "sortperm",
-    "AffineCompose", "abs2", "identity", "sqrt", "lib",
+    "AffineCompose", "abs2", "identity", "sqrt", "prod", "sqdiff", "wsq", "lib",
 ]

@@ -22,6 +22,7 @@ U8, I8, U16, I16, U32, I32, U64, I64, F32, F64 = range(10)
 MAP_IDENTITY, MAP_ABS2, MAP_ABS = range(3)
 OP_ADD, OP_MUL, OP_MIN, OP_MAX, OP_AND, OP_OR, OP_XOR, OP_AFFINE = range(8)
 POST_IDENTITY, POST_SQRT = range(2)
+MAPN_PROD, MAPN_SQDIFF, MAPN_WSQ = range(3)
 PRIM_MAPREDUCE, PRIM_SCAN, PRIM_SORT_KEYS, PRIM_SORT_PAIRS = range(4)
 
 
@@ -50,6 +51,8 @@ PROTOTYPES = {
     "kf_mapreduce_workspace_bytes": (c_size_t, [c_int32, c_uint64, POINTER(LaunchCfg)]),
     "kf_mapreduce": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_void_p, c_uint64, c_void_p,
                                c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
+    "kf_mapreduce_multi": (c_int32, [c_int32, c_int32, c_int32, c_int32, POINTER(c_void_p), c_int32, c_uint64, c_void_p,
+                                     c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_scan_workspace_bytes": (c_size_t, [c_int32, c_int32, c_uint64, POINTER(LaunchCfg)]),
     "kf_scan": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_void_p, c_uint64, c_void_p,
                           c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),

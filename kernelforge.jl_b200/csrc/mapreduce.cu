@@ -11,48 +11,9 @@
 // Follows the semantics of mapreduce1d_kernel! (src/mapreduce/1D/mapreduce1d_kernel.jl:5-94 of
 // KernelForge.jl): accumulate in the element type, strided order (op must be commutative), g
 // applied once at the end.
-#include "common.cuh"
-
-#include <type_traits>
+#include "mapreduce_impl.cuh"
 
 namespace kf {
-
-template <typename Op, typename T> __device__ __forceinline__ T warp_reduce(T v) {
-    if constexpr (sizeof(T) == 4 && !IsFloat<T>::value) {
-        // redux.sync: single-instruction warp reductions for 32-bit integers.
-        if constexpr (std::is_same<Op, OpAdd>::value) return (T)__reduce_add_sync(0xFFFFFFFFu, (unsigned)v);
-        else if constexpr (std::is_same<Op, OpAnd>::value) return (T)__reduce_and_sync(0xFFFFFFFFu, (unsigned)v);
-        else if constexpr (std::is_same<Op, OpOr>::value) return (T)__reduce_or_sync(0xFFFFFFFFu, (unsigned)v);
-        else if constexpr (std::is_same<Op, OpXor>::value) return (T)__reduce_xor_sync(0xFFFFFFFFu, (unsigned)v);
-        else if constexpr (std::is_same<Op, OpMin>::value) return (T)__reduce_min_sync(0xFFFFFFFFu, v);
-        else if constexpr (std::is_same<Op, OpMax>::value) return (T)__reduce_max_sync(0xFFFFFFFFu, v);
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) v = Op::template apply<T>(v, shfl_down(v, d));
-    return v;
-}
-
-// CTA-wide reduction; the result is valid in thread 0.
-template <typename Op, typename T, int THREADS> __device__ __forceinline__ T block_reduce(T v, T *smem) {
-    constexpr int WARPS = THREADS / 32;
-    const u32 lane = lane_id(), warp = threadIdx.x >> 5;
-    v = warp_reduce<Op, T>(v);
-    if (lane == 0) smem[warp] = v;
-    __syncthreads();
-    if (warp == 0) {
-        v = lane < WARPS ? smem[lane] : Op::template identity<T>();
-        v = warp_reduce<Op, T>(v);
-    }
-    __syncthreads();
-    return v;
-}
-
-template <typename T> __device__ __forceinline__ T apply_post(int g, T x) {
-    if constexpr (IsFloat<T>::value) {
-        if (g == KF_POST_SQRT) return (T)sqrt((double)x);
-    }
-    return x;
-}
 
 template <typename T, typename Op, int THREADS, int UNROLL>
 __global__ void __launch_bounds__(THREADS)

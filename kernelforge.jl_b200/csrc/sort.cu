@@ -29,6 +29,10 @@ struct KeyInfo {
 };
 static bool key_info(int dtype, KeyInfo *k) {
     switch (dtype) {
+    case KF_U8: *k = {1, false, false}; return true;
+    case KF_I8: *k = {1, false, true}; return true;
+    case KF_U16: *k = {2, false, false}; return true;
+    case KF_I16: *k = {2, false, true}; return true;
     case KF_U32: *k = {4, false, false}; return true;
     case KF_I32: *k = {4, false, true}; return true;
     case KF_F32: *k = {4, true, true}; return true;
@@ -98,17 +102,32 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
     void *vscratch = base + p.off_vals;
 
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, p.clear_bytes, s));
-    rc = k.bytes == 4 ? sort_hist_k32(k.is_float, keys_src, n, ghist, k.signed_or_float, s)
-                      : sort_hist_k64(k.is_float, keys_src, n, ghist, k.signed_or_float, s);
+    switch (k.bytes) {
+    case 1: rc = sort_hist_k8(keys_src, n, ghist, k.signed_or_float, s); break;
+    case 2: rc = sort_hist_k16(keys_src, n, ghist, k.signed_or_float, s); break;
+    case 4: rc = sort_hist_k32(k.is_float, keys_src, n, ghist, k.signed_or_float, s); break;
+    default: rc = sort_hist_k64(k.is_float, keys_src, n, ghist, k.signed_or_float, s); break;
+    }
     if (rc != KF_OK) return rc;
     sort_scan_histogram_kernel<<<k.bytes, kRadix, 0, s>>>(ghist);
     KF_CUDA_TRY(cudaGetLastError());
 
     // Ping-pong plan: pass p writes dst when the number of passes still to come is even, else the
     // scratch; pass 0 reads src. With an even pass count this never writes src unless dst == src,
-    // and the last pass always lands in dst.
+    // and the last pass always lands in dst. One-byte keys take a single pass, which would read and
+    // write the same array when sorting in place: that case starts from a copy in the scratch.
     const int P = k.bytes;
     const void *kin = keys_src, *vin = vals_src;
+    if (P % 2 == 1) {
+        if (keys_dst == keys_src) {
+            KF_CUDA_TRY(cudaMemcpyAsync(kscratch, keys_src, n * k.bytes, cudaMemcpyDeviceToDevice, s));
+            kin = kscratch;
+        }
+        if (val_bytes && vals_dst == vals_src) {
+            KF_CUDA_TRY(cudaMemcpyAsync(vscratch, vals_src, n * val_bytes, cudaMemcpyDeviceToDevice, s));
+            vin = vscratch;
+        }
+    }
     for (int pass = 0; pass < P; ++pass) {
         const bool to_dst = ((P - 1 - pass) % 2) == 0;
         void *kout = to_dst ? keys_dst : kscratch;
@@ -127,8 +146,12 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
         a.shift = 8 * pass;
         a.top_xor = (pass == P - 1 && k.signed_or_float) ? 0x80u : 0u;
         a.signed_or_float = k.signed_or_float;
-        rc = k.bytes == 4 ? sort_pass_k32(k.is_float, val_bytes, p.variant, a, s)
-                          : sort_pass_k64(k.is_float, val_bytes, p.variant, a, s);
+        switch (k.bytes) {
+        case 1: rc = sort_pass_k8(val_bytes, p.variant, a, s); break;
+        case 2: rc = sort_pass_k16(val_bytes, p.variant, a, s); break;
+        case 4: rc = sort_pass_k32(k.is_float, val_bytes, p.variant, a, s); break;
+        default: rc = sort_pass_k64(k.is_float, val_bytes, p.variant, a, s); break;
+        }
         if (rc != KF_OK) return rc;
         kin = kout;
         vin = vout;

@@ -478,6 +478,11 @@ int sort_pass_k32(bool is_float, int val_bytes, int variant, const SortPassArgs 
 int sort_pass_k64(bool is_float, int val_bytes, int variant, const SortPassArgs &a, cudaStream_t s);
 int sort_hist_k32(bool is_float, const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s);
 int sort_hist_k64(bool is_float, const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s);
+// 8- and 16-bit keys are integers only.
+int sort_pass_k8(int val_bytes, int variant, const SortPassArgs &a, cudaStream_t s);
+int sort_pass_k16(int val_bytes, int variant, const SortPassArgs &a, cudaStream_t s);
+int sort_hist_k8(const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s);
+int sort_hist_k16(const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s);
 
 #define KF_SORT_INSTANTIATE(NAME, KeyT)                                                               \
     namespace kf {                                                                                    \
@@ -497,6 +502,19 @@ int sort_hist_k64(bool is_float, const void *keys, u64 n, u64 *ghist, int sof, c
     int sort_hist_##NAME(bool is_float, const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s) { \
         return is_float ? histogram_launch<KeyT, true>(keys, n, ghist, sof, s)                        \
                         : histogram_launch<KeyT, false>(keys, n, ghist, sof, s);                      \
+    }                                                                                                 \
+    }
+
+#define KF_SORT_INSTANTIATE_INT(NAME, KeyT)                                                           \
+    namespace kf {                                                                                    \
+    int sort_pass_##NAME(int val_bytes, int variant, const SortPassArgs &a, cudaStream_t s) {         \
+        if (val_bytes == 0) return onesweep_launch<KeyT, false, void>(variant, a, s);                 \
+        if (val_bytes == 4) return onesweep_launch<KeyT, false, uint32_t>(variant, a, s);             \
+        if (val_bytes == 8) return onesweep_launch<KeyT, false, u64>(variant, a, s);                  \
+        return KF_ERR_UNSUPPORTED;                                                                    \
+    }                                                                                                 \
+    int sort_hist_##NAME(const void *keys, u64 n, u64 *ghist, int sof, cudaStream_t s) {              \
+        return histogram_launch<KeyT, false>(keys, n, ghist, sof, s);                                 \
     }                                                                                                 \
     }
 

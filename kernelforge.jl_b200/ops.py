@@ -8,6 +8,7 @@ operator set; the host layer recognises the supported functions by identity and 
     +  -> operator.add       *  -> operator.mul      min / max -> builtins.min / max
     &  -> operator.and_      |  -> operator.or_      xor (⊻) -> operator.xor
     sqrt (as g) -> math.sqrt / sqrt
+    (a, b, ...) -> a*b*...  -> prod / operator.mul     (a, b) -> (a-b)^2 -> sqdiff     (w, x) -> w*x*x -> wsq
     AffineCompose() -> the non-commutative composition of affine maps (new in this library)
 
 Strings ("+", "min", "abs2", ...) are accepted as well.
@@ -36,6 +37,24 @@ def abs2(x):
 def sqrt(x):
     """Julia's `sqrt` (usable as the post-map `g` of mapreduce)."""
     return math.sqrt(x)
+
+
+def prod(*xs):
+    """Map over a tuple of arrays: x1*x2*...*xk (`(a, b) -> a * b` is the dot product)."""
+    r = xs[0]
+    for x in xs[1:]:
+        r = r * x
+    return r
+
+
+def sqdiff(a, b):
+    """Map over two arrays: (a - b)^2."""
+    return (a - b) * (a - b)
+
+
+def wsq(w, x):
+    """Map over two arrays: w * x * x (weighted sum of squares)."""
+    return w * x * x
 
 
 class AffineCompose:
@@ -70,6 +89,10 @@ _POSTS = {identity: C.POST_IDENTITY, math.sqrt: C.POST_SQRT, sqrt: C.POST_SQRT, 
           "identity": C.POST_IDENTITY, "sqrt": C.POST_SQRT, None: C.POST_IDENTITY}
 
 
+_MAPNS = {prod: C.MAPN_PROD, operator.mul: C.MAPN_PROD, torch.mul: C.MAPN_PROD, "prod": C.MAPN_PROD, "*": C.MAPN_PROD,
+          sqdiff: C.MAPN_SQDIFF, "sqdiff": C.MAPN_SQDIFF, wsq: C.MAPN_WSQ, "wsq": C.MAPN_WSQ}
+
+
 def _lookup(table, fn, what):
     try:
         if fn in table:
@@ -83,6 +106,10 @@ def _lookup(table, fn, what):
 
 def map_code(f) -> int:
     return _lookup(_MAPS, f, "map function f")
+
+
+def mapn_code(f) -> int:
+    return _lookup(_MAPNS, f, "map function f over a tuple of arrays")
 
 
 def op_code(op) -> int:

@@ -21,7 +21,7 @@ from . import _cabi as C
 from . import ops
 from .allocations import Sort1D, resolve_tmp, sort_bytes
 
-_SORT_KEY_CODES = {C.U32, C.I32, C.F32, C.U64, C.I64, C.F64}
+_SORT_KEY_CODES = {C.U8, C.I8, C.U16, C.I16, C.U32, C.I32, C.F32, C.U64, C.I64, C.F64}
 
 
 def _reject(by, uint_map, lt, rev, algorithm):

@@ -181,6 +181,29 @@ def np_mapreduce(f: int, op: int, x: np.ndarray):
     return np_scan(f, op, x)[-1]
 
 
+MAPN_PROD, MAPN_SQDIFF, MAPN_WSQ = range(3)
+
+
+def np_mapreduce_multi(fn: int, op: int, arrays, post_sqrt: bool = False):
+    """Tuple form mapreduce(f, op, (x1, ..., xk)) as the reference's tests state it
+    (test/tests/mapreduce/mapreduce1d_test.jl:106-194): floats are mapped and folded in Float64,
+    integers in the element type (wrapping)."""
+    xs = [_c(a) for a in arrays]
+    if xs[0].dtype.kind == "f":
+        xs = [a.astype(np.float64) for a in xs]
+    with np.errstate(over="ignore"):
+        if fn == MAPN_SQDIFF:
+            m = (xs[0] - xs[1]) * (xs[0] - xs[1])
+        elif fn == MAPN_WSQ:
+            m = xs[0] * xs[1] * xs[1]
+        else:
+            m = xs[0].copy()
+            for a in xs[1:]:
+                m = m * a
+        r = _NP_OPS[op].reduce(m, dtype=m.dtype)
+    return np.sqrt(r) if post_sqrt else r
+
+
 # ---- timed CPU baseline (Base-like) ----------------------------------------------------------------
 def max_threads() -> int:
     return int(lib().kfo_max_threads())

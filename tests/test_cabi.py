@@ -58,7 +58,8 @@ def test_workspace_queries(kf):
     keys = lib.kf_sort_workspace_bytes(C.U32, 0, n, None)
     pairs = lib.kf_sort_workspace_bytes(C.U32, 4, n, None)
     assert keys >= 4 * n and pairs >= 8 * n and pairs > keys  # n-element ping-pong scratch inside
-    assert lib.kf_sort_workspace_bytes(C.U16, 0, n, None) == 0  # not a radix key type of this library
+    assert lib.kf_sort_workspace_bytes(C.U16, 0, n, None) >= 2 * n  # every element type is a key type
+    assert lib.kf_sort_workspace_bytes(42, 0, n, None) == 0
     assert lib.kf_sort_workspace_bytes(C.U32, 3, n, None) == 0
     bad = ctypes.pointer(C.LaunchCfg(96, 3, 0, 0))
     assert lib.kf_scan_workspace_bytes(C.F32, 0, n, bad) == 0
@@ -93,7 +94,8 @@ def test_argument_errors_before_any_device_work(kf):
     assert lib.kf_scan(0, 0, C.F32, fake, fake, 1 << 20, None, fake, 8, None, None) == C.ERR_WORKSPACE_TOO_SMALL
     assert lib.kf_scan(0, 0, 42, fake, fake, 10, None, fake, 1 << 20, None, None) == C.ERR_INVALID_ARG
     assert lib.kf_sort_keys(C.U32, fake, fake, 0, fake, 0, None, None) == C.OK
-    assert lib.kf_sort_keys(C.U8, fake, fake, 10, fake, 1 << 20, None, None) == C.ERR_UNSUPPORTED
+    assert lib.kf_sort_keys(42, fake, fake, 10, fake, 1 << 20, None, None) == C.ERR_INVALID_ARG
+    assert lib.kf_sort_pairs(C.U8, fake, fake, 2, fake, fake, 10, fake, 1 << 20, None, None) == C.ERR_UNSUPPORTED  # 2-byte payload
     assert lib.kf_sort_keys(C.U32, fake, fake, 1 << 20, fake, 1024, None, None) == C.ERR_WORKSPACE_TOO_SMALL
     assert lib.kf_sort_pairs(C.U32, fake, fake, 0, fake, fake, 10, fake, 1 << 20, None, None) == C.ERR_INVALID_ARG
     assert lib.kf_sort_pairs(C.U32, fake, fake, 4, None, fake, 10, fake, 1 << 30, None, None) == C.ERR_INVALID_ARG

@@ -133,6 +133,56 @@ def test_errors(kf):
     assert kf.mapreduce(kf.identity, "+", x) == 100.0  # the context survives the rejected calls
 
 
+def test_tuple_inputs_dot_family(kf, oracle):
+    """The tuple form (test/tests/mapreduce/mapreduce1d_test.jl:106-194): dot product, weighted sum of
+    squares, squared distance with g=sqrt, three arrays, a reused workspace; Float64 as there, plus
+    Float32 and integers (bit-exact, wrapping)."""
+    rng = np.random.default_rng(5)
+    for dtype in (np.float64, np.float32):
+        tol = 1e-12 if dtype == np.float64 else 2e-5
+        for n in (1, 10_001, 50_000, 1_000_003):
+            x, y, z = (rng.random(n).astype(dtype) for _ in range(3))
+            dx, dy, dz = to_dev(x), to_dev(y), to_dev(z)
+            cases = [(kf.prod, (dx, dy), oracle.np_mapreduce_multi(oracle.MAPN_PROD, 0, (x, y)), kf.identity),
+                     (kf.wsq, (dx, dy), oracle.np_mapreduce_multi(oracle.MAPN_WSQ, 0, (x, y)), kf.identity),
+                     (operator.mul, (dx, dy), oracle.np_mapreduce_multi(oracle.MAPN_PROD, 0, (x, y), True), kf.sqrt),
+                     (kf.sqdiff, (dx, dy), oracle.np_mapreduce_multi(oracle.MAPN_SQDIFF, 0, (x, y), True), math.sqrt),
+                     (kf.prod, (dx, dy, dz), oracle.np_mapreduce_multi(oracle.MAPN_PROD, 0, (x, y, z)), kf.identity)]
+            for f, srcs, ref, g in cases:
+                got = kf.mapreduce1d(f, "+", srcs, g=g)
+                assert abs(got - ref) <= tol * max(1.0, math.log2(n + 1)) * abs(ref), (dtype, n, got, ref)
+            assert kf.mapreduce(kf.prod, "max", (dx, dy)) == pytest.approx(float((x.astype(np.float64) * y).max()), rel=1e-6)
+    # integers wrap in the element type
+    for dtype in (np.int32, np.uint8, np.int64):
+        info = np.iinfo(dtype)
+        a = rng.integers(info.min, info.max, 300_007, dtype=dtype, endpoint=True)
+        b = rng.integers(info.min, info.max, 300_007, dtype=dtype, endpoint=True)
+        got = kf.mapreduce(kf.prod, "+", (to_dev(a), to_dev(b)), to_cpu=False)
+        assert to_host(got)[0] == oracle.np_mapreduce_multi(oracle.MAPN_PROD, 0, (a, b))
+    # views that do not share their 16-byte misalignment take the element-wise path
+    x, y = rng.random(70_001), rng.random(70_003)
+    got = kf.mapreduce(kf.prod, "+", (to_dev(x)[1:], to_dev(y)[3:]))
+    assert got == pytest.approx(float((x[1:] * y[3:]).sum()), rel=1e-12)
+    got = kf.mapreduce(kf.prod, "+", (to_dev(x)[1:], to_dev(y)[1:70_001]))  # same misalignment: vector path with a head
+    assert got == pytest.approx(float((x[1:] * y[1:70_001]).sum()), rel=1e-12)
+    # in place with a pre-allocated tmp, reused across trials (:160-178)
+    n = 50_000
+    dst = torch.zeros(1, dtype=torch.float64, device="cuda")
+    dx, dy = to_dev(rng.random(n)), to_dev(rng.random(n))
+    tmp = kf.get_allocation(kf.MapReduce1D, kf.prod, "+", (dx, dy))
+    for trial in range(5):
+        x, y = rng.random(n), rng.random(n)
+        dx.copy_(to_dev(x)); dy.copy_(to_dev(y))
+        kf.mapreduce1d_(kf.prod, "+", dst, (dx, dy), tmp=tmp)
+        assert to_host(dst)[0] == pytest.approx(float((x * y).sum()), rel=1e-12)
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(lambda a, b: a + b, "+", (dx, dy))
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.prod, "+", (dx, dy[:10]))
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.sqdiff, "+", (dx, dy, dx))
+
+
 def test_full_size_2p28(kf):
     """n = 2^28: UInt32 wrapping sum bit-exact and Float32 sum within tolerance, checked against
     torch reductions in wider types on the same device data."""

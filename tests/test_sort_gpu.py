@@ -14,7 +14,7 @@ from util import bits, to_dev, to_host
 
 pytestmark = pytest.mark.gpu
 
-KEY_DTYPES = [np.uint32, np.int32, np.float32, np.uint64, np.int64, np.float64]
+KEY_DTYPES = [np.uint8, np.int8, np.uint16, np.int16, np.uint32, np.int32, np.float32, np.uint64, np.int64, np.float64]
 
 
 def rand_keys(dtype, n, rng):
@@ -99,7 +99,7 @@ def test_float_boundary_values(kf, oracle):
     assert_same_bits(to_host(kf.sort(to_dev(x64))), oracle.c_sort(x64))
 
 
-@pytest.mark.parametrize("key_dtype", [np.uint32, np.int32, np.float32, np.uint64, np.int64, np.float64])
+@pytest.mark.parametrize("key_dtype", [np.uint8, np.int16, np.uint32, np.int32, np.float32, np.uint64, np.int64, np.float64])
 @pytest.mark.parametrize("val_dtype", [np.int32, np.int64, np.float32, np.float64])
 def test_key_value(kf, oracle, key_dtype, val_dtype):
     """`keys` drives the order, `vals` follows: vals_out == vals[sortperm(keys)] (stable)."""
