@@ -19,8 +19,9 @@ static const ScanVariant kScanVariants[] = {
     {256, 4, false}, {512, 4, false}, {256, 8, false}, {128, 8, false},  // direct
     {768, 4, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead
     {640, 4, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead
+    {512, 8, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead (best for 2- and 8-byte elements)
 };
-constexpr int kNumScanVariants = 6;
+constexpr int kNumScanVariants = 7;
 constexpr int kScanFallbackVariant = 1;  // direct 512x4: what a ring variant falls back to
 
 struct ScanPlan {
@@ -59,7 +60,8 @@ int scan_launch_ring_one(const Access &acc, const Arrays &arr, const ScanArgs &a
 template <typename T, typename Op, typename Access, typename Arrays>
 int scan_launch(int variant, const Access &acc, const Arrays &arr, const ScanArgs &args, cudaStream_t s) {
     const unsigned grid = (unsigned)args.ntiles;
-    constexpr int RV = 4 / Arrays::NARR;  // ring vectors per thread and array
+    constexpr int RV = 4 / Arrays::NARR;   // ring vectors per thread and array
+    constexpr int RV8 = 8 / Arrays::NARR;
     switch (variant) {
     case 0: scan_kernel<T, Op, Access, 256, 4><<<grid, 256, 0, s>>>(acc, args); break;
     case 1: scan_kernel<T, Op, Access, 512, 4><<<grid, 512, 0, s>>>(acc, args); break;
@@ -67,6 +69,7 @@ int scan_launch(int variant, const Access &acc, const Arrays &arr, const ScanArg
     case 3: scan_kernel<T, Op, Access, 128, 8><<<grid, 128, 0, s>>>(acc, args); break;
     case 4: return scan_launch_ring_one<T, Op, Access, Arrays, 768, RV, 2, 3, 2>(acc, arr, args, s);
     case 5: return scan_launch_ring_one<T, Op, Access, Arrays, 640, RV, 2, 3, 1>(acc, arr, args, s);
+    case 6: return scan_launch_ring_one<T, Op, Access, Arrays, 512, RV8, 2, 3, 2>(acc, arr, args, s);
     default: return KF_ERR_UNSUPPORTED;
     }
     KF_CUDA_TRY(cudaGetLastError());

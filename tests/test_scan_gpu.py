@@ -96,7 +96,7 @@ def test_reused_tmp(kf, oracle, dtype, n):
         assert (to_host(dst) == np.cumsum(h, dtype=dtype)).all()  # small integers: exact in every type
 
 
-@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (256, 8), (128, 8), (768, 4), (640, 4)])
+@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (256, 8), (128, 8), (768, 4), (640, 4), (512, 8)])
 def test_launch_variants(kf, oracle, workgroup, nitem):
     """Every compiled variant: the direct kernels and the two persistent kernels (768, 640)."""
     x = np.random.default_rng(2).integers(0, 256, 3_000_017).astype(np.uint32)

@@ -145,7 +145,8 @@ def test_key_value_errors(kf):
         with pytest.raises(kf.ArgumentError):
             kf.sort(v, **bad)
     with pytest.raises(kf.ArgumentError):
-        kf.sort(v.to(torch.int16))
+        kf.sort(v.to(torch.float16))  # no radix mapping for this element type here
+    assert kf.sort(v.to(torch.int16)).dtype == torch.int16  # every integer width is a key type
 
 
 @pytest.mark.parametrize("workgroup,nitem", [(256, 16), (512, 16), (512, 24), (384, 24)])
