@@ -255,6 +255,15 @@ int32_t kf_iota(int32_t dtype, void *dst, uint64_t n, uint64_t start, kf_stream_
 int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t n,
                         const void *splitters, int32_t nsplit, uint64_t *out, kf_stream_t stream);
 
+/* out[i] (uint8) = number of splitters (ascending, same dtype as keys, at most 255) whose mapped key
+ * is smaller than that of keys[i]: the destination piece of key i when piece j holds the keys in
+ * (splitter[j-1], splitter[j]]. With kf_sort_pairs on these one-byte ids (one stable pass, the keys
+ * riding as the payload) it cuts an UNSORTED shard into per-destination runs for the sample sort.
+ * The reference has no multi-GPU layer; the closest code is the bucket assignment of its
+ * single-GPU sample sort (src/sort/sample_sort.jl:284-312). */
+int32_t kf_bucket_ids(int32_t key_dtype, const void *keys, uint64_t n,
+                      const void *splitters, int32_t nsplit, uint8_t *out, kf_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

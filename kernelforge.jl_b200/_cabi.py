@@ -68,6 +68,7 @@ PROTOTYPES = {
                                 c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_iota": (c_int32, [c_int32, c_void_p, c_uint64, c_uint64, c_void_p]),
     "kf_upper_bounds": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_int32, c_void_p, c_void_p]),
+    "kf_bucket_ids": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_int32, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -225,6 +225,16 @@ extern "C" int32_t kf_iota(int32_t dtype, void *dst, uint64_t n, uint64_t start,
     return KF_OK;
 }
 
+template <typename KeyT>
+static void launch_upper_bounds(const KeyInfo &k, const void *keys, u64 n, const void *splitters, int nsplit, u64 *out, cudaStream_t s) {
+    const int threads = 128, blocks = (nsplit + threads - 1) / threads;
+    if (k.is_float)
+        upper_bounds_kernel<KeyT, sizeof(KeyT) >= 4><<<blocks, threads, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out, true);
+    else
+        upper_bounds_kernel<KeyT, false><<<blocks, threads, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out,
+                                                                     k.signed_or_float);
+}
+
 extern "C" int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t n, const void *splitters,
                                    int32_t nsplit, uint64_t *out, kf_stream_t stream) {
     KeyInfo k;
@@ -232,13 +242,61 @@ extern "C" int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t
     if (nsplit <= 0) return KF_OK;
     if (!splitters || !out || (n && !keys)) return KF_ERR_INVALID_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = 128, blocks = (nsplit + threads - 1) / threads;
-    if (k.bytes == 4) {
-        if (k.is_float) upper_bounds_kernel<uint32_t, true><<<blocks, threads, 0, s>>>((const uint32_t *)keys, n, (const uint32_t *)splitters, nsplit, (u64 *)out, true);
-        else upper_bounds_kernel<uint32_t, false><<<blocks, threads, 0, s>>>((const uint32_t *)keys, n, (const uint32_t *)splitters, nsplit, (u64 *)out, k.signed_or_float);
-    } else {
-        if (k.is_float) upper_bounds_kernel<u64, true><<<blocks, threads, 0, s>>>((const u64 *)keys, n, (const u64 *)splitters, nsplit, (u64 *)out, true);
-        else upper_bounds_kernel<u64, false><<<blocks, threads, 0, s>>>((const u64 *)keys, n, (const u64 *)splitters, nsplit, (u64 *)out, k.signed_or_float);
+    switch (k.bytes) {
+    case 1: launch_upper_bounds<uint8_t>(k, keys, n, splitters, nsplit, (u64 *)out, s); break;
+    case 2: launch_upper_bounds<uint16_t>(k, keys, n, splitters, nsplit, (u64 *)out, s); break;
+    case 4: launch_upper_bounds<uint32_t>(k, keys, n, splitters, nsplit, (u64 *)out, s); break;
+    default: launch_upper_bounds<u64>(k, keys, n, splitters, nsplit, (u64 *)out, s); break;
+    }
+    KF_CUDA_TRY(cudaGetLastError());
+    return KF_OK;
+}
+
+// out[i] = number of splitters whose mapped key is smaller than that of keys[i]: the destination of
+// key i in a sample sort whose piece j holds the keys in (splitter[j-1], splitter[j]].
+template <typename KeyT, bool IS_FLOAT>
+__global__ void __launch_bounds__(256) bucket_ids_kernel(const KeyT *keys, u64 n, const KeyT *splitters, int nsplit, uint8_t *out, bool sof) {
+    __shared__ KeyT s_split[256];
+    for (int j = threadIdx.x; j < nsplit; j += blockDim.x) s_split[j] = mapped_key<KeyT, IS_FLOAT>(splitters[j], sof);
+    __syncthreads();
+    const u64 stride = (u64)gridDim.x * blockDim.x;
+    for (u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const KeyT m = mapped_key<KeyT, IS_FLOAT>(keys[i], sof);
+        int lo = 0, hi = nsplit;  // first splitter that is >= m
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (s_split[mid] < m) lo = mid + 1;
+            else hi = mid;
+        }
+        out[i] = (uint8_t)lo;
+    }
+}
+
+template <typename KeyT>
+static void launch_bucket_ids(const KeyInfo &k, const void *keys, u64 n, const void *splitters, int nsplit, uint8_t *out, cudaStream_t s) {
+    u64 blocks = (n + 255) / 256;
+    const u64 cap = (u64)device_sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (k.is_float)
+        bucket_ids_kernel<KeyT, sizeof(KeyT) >= 4><<<(unsigned)blocks, 256, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out, true);
+    else
+        bucket_ids_kernel<KeyT, false><<<(unsigned)blocks, 256, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out,
+                                                                         k.signed_or_float);
+}
+
+extern "C" int32_t kf_bucket_ids(int32_t key_dtype, const void *keys, uint64_t n, const void *splitters, int32_t nsplit,
+                                 uint8_t *out, kf_stream_t stream) {
+    KeyInfo k;
+    if (!key_info(key_dtype, &k)) return KF_ERR_UNSUPPORTED;
+    if (nsplit < 0 || nsplit > 255) return KF_ERR_INVALID_ARG;
+    if (n == 0) return KF_OK;
+    if (!keys || !out || (nsplit && !splitters)) return KF_ERR_INVALID_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (k.bytes) {
+    case 1: launch_bucket_ids<uint8_t>(k, keys, n, splitters, nsplit, out, s); break;
+    case 2: launch_bucket_ids<uint16_t>(k, keys, n, splitters, nsplit, out, s); break;
+    case 4: launch_bucket_ids<uint32_t>(k, keys, n, splitters, nsplit, out, s); break;
+    default: launch_bucket_ids<u64>(k, keys, n, splitters, nsplit, out, s); break;
     }
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;

@@ -10,10 +10,13 @@ rank owns one contiguous shard of a global array (rank order = array order) and 
               rank order -> local scan seeded with the carry (12n bytes instead of the 16n of
               "scan, then fix up"). Non-commutative operators (AffineCompose) take the ordered
               route: local scan for the total, then the seeded scan.
-  sort      : local onesweep sort -> 1024 regular samples per rank, allgather, identical splitter
-              choice everywhere -> cut the sorted shard at the splitters (kf_upper_bounds) ->
-              all-to-all of the runs (NCCL, over NVLink) -> local onesweep sort of the received
-              runs (keys only, so re-sorting is bit-exact and stable order is irrelevant).
+  sort      : samples of the shard, allgather, identical splitter choice everywhere -> cut the shard
+              into one run per destination -> all-to-all of the runs (NCCL, over NVLink) -> local
+              onesweep sort of what arrived (keys only, so stable order is irrelevant and the result
+              is bit-exact). The cut is "partition first" for 4- and 8-byte keys: destination ids
+              (kf_bucket_ids) and ONE stable radix pass on those one-byte ids with the keys as the
+              payload, about 0.4 of a full local sort; other key widths sort the shard first and
+              cut it with kf_upper_bounds.
 
 Remote data always lands in local HBM through NCCL before a kernel touches it. The local steps go
 through `LocalOps`, whose default implementation calls the CUDA kernels; the CPU tests of the
@@ -69,6 +72,20 @@ class LocalOps:
                                           ops.stream_handle(sorted_keys))
         C.check(rc, "upper_bounds")
         return out
+
+    def bucket_ids(self, x, splitters):
+        """uint8 destination of every key: the number of splitters below it (in the sort's key order)."""
+        out = torch.empty(x.numel(), dtype=torch.uint8, device=x.device)
+        with torch.cuda.device(x.device):
+            rc = C.load().kf_bucket_ids(ops.dtype_code(x), x.data_ptr(), x.numel(), splitters.data_ptr(),
+                                        splitters.numel(), out.data_ptr(), ops.stream_handle(x))
+        C.check(rc, "bucket_ids")
+        return out
+
+    def partition(self, ids, x):
+        """x arranged by destination id (stable), and the sorted ids."""
+        vals, keys = _sort_(torch.empty_like(x), x, keys=ids, keys_dst=torch.empty_like(ids))
+        return vals, keys
 
     def take(self, x, positions):
         """x[positions] for a small index tensor (sample extraction). torch cannot index unsigned
@@ -150,22 +167,44 @@ def choose_splitters(sorted_samples, world: int):
     return _bits_view(sorted_samples)[pos].view(sorted_samples.dtype)
 
 
-def sort(group: ShardGroup, x, *, local: LocalOps = _DEFAULT_OPS, samples_per_rank: int = SAMPLES_PER_RANK):
+def sample_positions(n: int, s: int, device):
+    """s positions in [0, n): one per stratum of n/s elements, at a low-discrepancy offset inside it
+    (so that periodic data does not alias with the stride)."""
+    i = torch.arange(s, device=device, dtype=torch.float64)
+    jitter = torch.remainder(i * 0.6180339887498949 + 0.5, 1.0)
+    return ((i + jitter) * (n / s)).to(torch.int64).clamp_(0, max(n - 1, 0))
+
+
+def sort(group: ShardGroup, x, *, local: LocalOps = _DEFAULT_OPS, samples_per_rank: int = SAMPLES_PER_RANK,
+         partition_first=None):
     """Sample sort of the sharded keys `x`. Returns (sorted_chunk, counts): rank r holds the r-th
-    contiguous piece of the globally sorted array; `counts` (host list) are the piece lengths."""
+    contiguous piece of the globally sorted array; `counts` (host list) are the piece lengths.
+    `partition_first` (default: for 4- and 8-byte keys) cuts the unsorted shard with one radix pass
+    instead of sorting it first."""
     world, rank = group.world, group.rank
     n = x.numel()
-    mine = local.sort(x)
     if world == 1:
-        return mine, [n]
-    # 1. regular samples of the sorted shard
+        return local.sort(x), [n]
+    if partition_first is None:
+        partition_first = x.element_size() in (4, 8) and world <= 256
     s = samples_per_rank
-    pos = ((torch.arange(s, device=x.device, dtype=torch.float64) + 0.5) * (n / s)).to(torch.int64).clamp_(0, max(n - 1, 0))
-    samples = local.take(mine, pos) if n > 0 else torch.zeros(s, dtype=x.dtype, device=x.device)
-    all_samples = local.sort(all_gather_vec(group, samples))
-    splitters = choose_splitters(all_samples, world)
-    # 2. cut the sorted shard: run j goes to rank j
-    cuts = local.upper_bounds(mine, splitters)
+    if partition_first:
+        # 1. samples of the unsorted shard (4x oversampled: they are not regular samples of a sorted run)
+        s = 4 * samples_per_rank
+        samples = local.take(x, sample_positions(n, s, x.device)) if n > 0 else torch.zeros(s, dtype=x.dtype, device=x.device)
+        splitters = choose_splitters(local.sort(all_gather_vec(group, samples)), world)
+        # 2. destination of every key, then one stable pass by destination
+        mine, ids = local.partition(local.bucket_ids(x, splitters), x)
+        dest = torch.arange(world - 1, dtype=torch.uint8, device=x.device)
+        cuts = local.upper_bounds(ids, dest)
+    else:
+        # 1. regular samples of the sorted shard
+        mine = local.sort(x)
+        pos = ((torch.arange(s, device=x.device, dtype=torch.float64) + 0.5) * (n / s)).to(torch.int64).clamp_(0, max(n - 1, 0))
+        samples = local.take(mine, pos) if n > 0 else torch.zeros(s, dtype=x.dtype, device=x.device)
+        splitters = choose_splitters(local.sort(all_gather_vec(group, samples)), world)
+        # 2. cut the sorted shard: run j goes to rank j
+        cuts = local.upper_bounds(mine, splitters)
     bounds = torch.cat([torch.zeros(1, dtype=torch.int64, device=x.device), cuts,
                         torch.full((1,), n, dtype=torch.int64, device=x.device)])
     send_counts = bounds[1:] - bounds[:-1]
@@ -176,7 +215,7 @@ def sort(group: ShardGroup, x, *, local: LocalOps = _DEFAULT_OPS, samples_per_ra
     inbox = torch.empty(sum(recv), dtype=x.dtype, device=x.device)
     dist.all_to_all_single(_bits_view(inbox), _bits_view(mine), output_split_sizes=recv, input_split_sizes=send,
                            group=group.group)
-    # 4. merge = one more local sort of the received sorted runs
+    # 4. one local sort of what arrived
     out = local.sort(inbox) if inbox.numel() else inbox
     counts = [int(v) for v in count_matrix.sum(dim=0)]
     return out, counts

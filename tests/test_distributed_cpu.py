@@ -60,6 +60,14 @@ class HostOps:
     def upper_bounds(self, sorted_keys, splitters):
         return torch.from_numpy(np.searchsorted(sorted_keys.numpy(), splitters.numpy(), side="right").astype(np.int64))
 
+    def bucket_ids(self, x, splitters):
+        u = self.O.np_uint_map(x.numpy())
+        return torch.from_numpy(np.searchsorted(self.O.np_uint_map(splitters.numpy()), u, side="left").astype(np.uint8))
+
+    def partition(self, ids, x):
+        p = np.argsort(ids.numpy(), kind="stable")
+        return x[torch.from_numpy(p)], ids[torch.from_numpy(p)]
+
     def take(self, x, positions):
         return x[positions]
 
@@ -101,10 +109,12 @@ def _worker(rank, world, port, n_per, tmpdir):
 
         keys = rng.integers(0, 1 << 31, n).astype(np.int32)
         keys[::5] = 7  # a heavy duplicate straddling the splitters
-        chunk, counts = kfd.sort(group, torch.from_numpy(keys[lo:hi]), local=host, samples_per_rank=64)
-        assert sum(counts) == n and counts[rank] == chunk.numel()
-        off = sum(counts[:rank])
-        assert (chunk.numpy() == np.sort(keys)[off:off + counts[rank]]).all()
+        for first in (True, False):  # cut the unsorted shard with one pass / sort it first
+            chunk, counts = kfd.sort(group, torch.from_numpy(keys[lo:hi]), local=host, samples_per_rank=64, partition_first=first)
+            assert sum(counts) == n and counts[rank] == chunk.numel()
+            off = sum(counts[:rank])
+            assert (chunk.numpy() == np.sort(keys)[off:off + counts[rank]]).all()
+            assert max(counts) < 2.0 * n / world  # the heavy duplicate (20 % of the keys) lands in one piece
         with open(os.path.join(tmpdir, "ok%d" % rank), "w") as fh:
             fh.write("ok")
     finally:

@@ -62,10 +62,19 @@ def _worker(rank, world, port, n_per, tmpdir):
 
         keys = rng.integers(0, 1 << 32, n, dtype=np.uint64).astype(np.uint32)
         keys[::7] = 12345  # a heavy duplicate
-        chunk, counts = kfd.sort(group, dev(keys[lo:hi].view(np.int32)).view(torch.uint32))
-        assert sum(counts) == n and counts[rank] == chunk.numel()
+        for first in (True, False):  # cut the unsorted shard with one pass / sort it first
+            chunk, counts = kfd.sort(group, dev(keys[lo:hi].view(np.int32)).view(torch.uint32), partition_first=first)
+            assert sum(counts) == n and counts[rank] == chunk.numel()
+            off = sum(counts[:rank])
+            assert (chunk.view(torch.int32).cpu().numpy().view(np.uint32) == np.sort(keys)[off:off + counts[rank]]).all()
+        fk = rng.standard_normal(n).astype(np.float32)  # float keys: order by the mapped bits
+        chunk, counts = kfd.sort(group, dev(fk[lo:hi]))
         off = sum(counts[:rank])
-        assert (chunk.view(torch.int32).cpu().numpy().view(np.uint32) == np.sort(keys)[off:off + counts[rank]]).all()
+        assert (chunk.cpu().numpy().view(np.uint32) == np.sort(fk)[off:off + counts[rank]].view(np.uint32)).all()
+        k16 = rng.integers(-30000, 30000, n).astype(np.int16)  # 2-byte keys take the sort-first route
+        chunk, counts = kfd.sort(group, dev(k16[lo:hi]))
+        off = sum(counts[:rank])
+        assert (chunk.cpu().numpy() == np.sort(k16)[off:off + counts[rank]]).all()
         torch.cuda.synchronize()
         with open(os.path.join(tmpdir, "ok%d" % rank), "w") as fh:
             fh.write("ok")
