@@ -264,6 +264,43 @@ int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t n,
 int32_t kf_bucket_ids(int32_t key_dtype, const void *keys, uint64_t n,
                       const void *splitters, int32_t nsplit, uint8_t *out, kf_stream_t stream);
 
+/* ---- callers one step out: search, copy, fill ------------------------------------------------ */
+
+/* Comparison of an element with a scalar operand, for kf_find. */
+typedef enum kf_pred {
+    KF_PRED_GT = 0, KF_PRED_LT = 1, KF_PRED_GE = 2, KF_PRED_LE = 3, KF_PRED_EQ = 4, KF_PRED_NE = 5
+} kf_pred;
+
+/* Workspace for kf_argmax: per-CTA (value, index) partials + a completion counter. Replaces
+ * get_allocation(ArgMax1D, ...) (src/search/argmax.jl:117-150). */
+size_t kf_argmax_workspace_bytes(int32_t dtype, uint64_t n);
+
+/* out_index[0] (uint64, 0-based) = index of the first element whose f(src[i]) is extremal:
+ * `greater` != 0 is rel = `>` (argmax), 0 is rel = `<` (argmin); ties go to the smallest index.
+ * out_value (may be NULL) receives the extremal f(src[i]). One launch, last-CTA fold.
+ * Replaces argmax1d / argmax1d! (src/search/argmax.jl:8-86,153-270) and argmax_kernel!
+ * (src/search/argmax_kernel.jl:1-148). n == 0 returns KF_ERR_EMPTY_REDUCTION. */
+int32_t kf_argmax(int32_t f, int32_t greater, int32_t dtype, const void *src, uint64_t n,
+                  void *out_value, uint64_t *out_index, void *ws, size_t ws_bytes, kf_stream_t stream);
+
+/* out_index[0] (uint64, device) = index (0-based) of the first (`last` == 0) or last (`last` != 0)
+ * element with `src[i] pred operand`; `operand` is a HOST pointer to one element of `dtype`.
+ * Not found: first -> UINT64_MAX, last -> 0 with found indices stored as index + 1 (so 0 means
+ * none). CTAs stop early once a match ahead of them is known.
+ * Replaces findfirst / findlast (src/search/findfirst.jl:3-110) and findfirst_kernel!
+ * (src/search/findfirst_kernel.jl:1-67) for comparison predicates. */
+int32_t kf_find(int32_t pred, int32_t last, int32_t dtype, const void *src, uint64_t n,
+                const void *operand, uint64_t *out_index, kf_stream_t stream);
+
+/* dst[0 .. nbytes) = src[0 .. nbytes) with 128-bit streaming accesses (element-wise when the two
+ * arrays do not share their 16-byte misalignment). The roofline calibration kernel.
+ * Replaces vcopy! (src/copy/copy.jl:1-28, src/copy/copy_kernel.jl:1-18). */
+int32_t kf_vcopy(void *dst, const void *src, uint64_t nbytes, kf_stream_t stream);
+
+/* dst[i] = *value for i in [0, n); `value` is a HOST pointer to one element of `dtype`.
+ * Replaces setvalue! (src/copy/copy.jl:30-55, src/copy/copy_kernel.jl:20-36). */
+int32_t kf_setvalue(int32_t dtype, void *dst, uint64_t n, const void *value, kf_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -23,6 +23,7 @@ MAP_IDENTITY, MAP_ABS2, MAP_ABS = range(3)
 OP_ADD, OP_MUL, OP_MIN, OP_MAX, OP_AND, OP_OR, OP_XOR, OP_AFFINE = range(8)
 POST_IDENTITY, POST_SQRT = range(2)
 MAPN_PROD, MAPN_SQDIFF, MAPN_WSQ = range(3)
+PRED_GT, PRED_LT, PRED_GE, PRED_LE, PRED_EQ, PRED_NE = range(6)
 PRIM_MAPREDUCE, PRIM_SCAN, PRIM_SORT_KEYS, PRIM_SORT_PAIRS = range(4)
 
 
@@ -68,6 +69,11 @@ PROTOTYPES = {
                                 c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_iota": (c_int32, [c_int32, c_void_p, c_uint64, c_uint64, c_void_p]),
     "kf_upper_bounds": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_int32, c_void_p, c_void_p]),
+    "kf_argmax_workspace_bytes": (c_size_t, [c_int32, c_uint64]),
+    "kf_argmax": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "kf_find": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p]),
+    "kf_vcopy": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p]),
+    "kf_setvalue": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_void_p]),
     "kf_bucket_ids": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_int32, c_void_p, c_void_p]),
 }
 
