@@ -100,16 +100,25 @@ _NCCL_DTYPES = {torch.float32, torch.float64, torch.int32, torch.int64, torch.ui
 
 
 def _bits_view(t):
-    """Collectives move opaque bits: unsigned 16/32/64-bit tensors travel as their signed twins."""
+    """Unsigned 16/32/64-bit tensors as their signed twins (torch indexes and NCCL moves those)."""
     twin = {getattr(torch, "uint16", None): torch.int16, getattr(torch, "uint32", None): torch.int32,
             getattr(torch, "uint64", None): torch.int64}
     return t.view(twin[t.dtype]) if t.dtype in twin else t
 
 
+def _wire_view(t):
+    """What a collective carries: opaque bits. 2-byte integers travel as bytes (NCCL has no 16-bit
+    integer type); returns the view and the number of wire elements per element."""
+    t = _bits_view(t)
+    if t.dtype == torch.int16:
+        return t.view(torch.uint8), 2
+    return t, 1
+
+
 def all_gather_vec(group: ShardGroup, x):
     """Concatenation over ranks of equally sized 1-D tensors."""
     out = torch.empty(group.world * x.numel(), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(_bits_view(out), _bits_view(x.contiguous()), group=group.group)
+    dist.all_gather_into_tensor(_wire_view(out)[0], _wire_view(x.contiguous())[0], group=group.group)
     return out
 
 
@@ -213,8 +222,9 @@ def sort(group: ShardGroup, x, *, local: LocalOps = _DEFAULT_OPS, samples_per_ra
     recv = [int(v) for v in count_matrix[:, rank]]
     # 3. all-to-all of the runs
     inbox = torch.empty(sum(recv), dtype=x.dtype, device=x.device)
-    dist.all_to_all_single(_bits_view(inbox), _bits_view(mine), output_split_sizes=recv, input_split_sizes=send,
-                           group=group.group)
+    wire_in, per = _wire_view(inbox)
+    dist.all_to_all_single(wire_in, _wire_view(mine)[0], output_split_sizes=[per * v for v in recv],
+                           input_split_sizes=[per * v for v in send], group=group.group)
     # 4. one local sort of what arrived
     out = local.sort(inbox) if inbox.numel() else inbox
     counts = [int(v) for v in count_matrix.sum(dim=0)]

@@ -115,6 +115,10 @@ def _worker(rank, world, port, n_per, tmpdir):
             off = sum(counts[:rank])
             assert (chunk.numpy() == np.sort(keys)[off:off + counts[rank]]).all()
             assert max(counts) < 2.0 * n / world  # the heavy duplicate (20 % of the keys) lands in one piece
+        k16 = rng.integers(-30000, 30000, n).astype(np.int16)  # 2-byte keys: sort-first route, carried as bytes
+        chunk, counts = kfd.sort(group, torch.from_numpy(k16[lo:hi]), local=host, samples_per_rank=64)
+        off = sum(counts[:rank])
+        assert sum(counts) == n and (chunk.numpy() == np.sort(k16)[off:off + counts[rank]]).all()
         with open(os.path.join(tmpdir, "ok%d" % rank), "w") as fh:
             fh.write("ok")
     finally:
