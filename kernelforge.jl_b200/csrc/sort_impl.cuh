@@ -63,9 +63,10 @@ __device__ __forceinline__ u32 match_digit(u32 d) {
     u32 peers = 0xFFFFFFFFu;
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
-        const bool bit = (d >> b) & 1u;
-        const u32 m = __ballot_sync(0xFFFFFFFFu, bit);
-        peers &= bit ? m : ~m;
+        int mask;  // all ones when bit b of the digit is set, else zero
+        asm("bfe.s32 %0, %1, %2, 1;" : "=r"(mask) : "r"(d), "r"(b));
+        const u32 m = __ballot_sync(0xFFFFFFFFu, mask != 0);
+        peers &= ~(m ^ (u32)mask);  // lanes whose bit b equals mine: one three-input logic op
     }
     return peers;
 }
