@@ -297,3 +297,36 @@ def test_host_pipeline_chunk_ring(kf, oracle):
     pipe.scan_host("max", oc, hc)
     torch.cuda.synchronize()
     assert (oc.numpy().astype(np.float64) == oracle.c_scan(0, 3, c)).all()
+
+
+@pytest.mark.parametrize("workgroup,nitem", [(768, 4), (640, 4), (512, 8)])
+def test_persistent_kernel_edges(kf, oracle, workgroup, nitem):
+    """The persistent kernel forced onto sizes around its tile, ring and look-ahead boundaries: fewer
+    tiles than ring steps, exactly one tile, one element over, fewer tiles than CTAs, a few more; a
+    head tile (views off a 16-byte boundary by the same amount), in place, with a left seed."""
+    tile = workgroup * nitem * 4  # elements of 4 bytes per tile
+    rng = np.random.default_rng(workgroup)
+    for n in (1, 3, tile - 1, tile, tile + 1, 2 * tile, 3 * tile + 5, 4 * tile, 7 * tile - 3, 149 * tile + 7, 400 * tile + 1):
+        x = rng.integers(0, 1 << 32, n, dtype=np.uint32)
+        got = to_host(kf.scan("+", to_dev(x), workgroup=workgroup, Nitem=nitem))
+        assert (got == np.cumsum(x, dtype=np.uint32)).all(), n
+    for n in (tile // 2 + 1, 5 * tile // 2 + 3):  # 8-byte elements: half as many per tile
+        y = rng.integers(-1000, 1000, n).astype(np.int64)
+        assert (to_host(kf.scan("min", to_dev(y), workgroup=workgroup, Nitem=nitem)) == np.minimum.accumulate(y)).all()
+    n = 6 * tile + 11
+    x = rng.integers(0, 1 << 32, n, dtype=np.uint32)
+    for off in (1, 3):
+        src = to_dev(x, offset=off)
+        dst = to_dev(np.zeros(n, dtype=np.uint32), offset=off)
+        kf.scan_("+", dst, src, workgroup=workgroup, Nitem=nitem)
+        assert (to_host(dst) == np.cumsum(x, dtype=np.uint32)).all()
+    t = to_dev(x)
+    seed = to_dev(np.array([12345], dtype=np.uint32))
+    kf.scan_("+", t, t, init=seed, workgroup=workgroup, Nitem=nitem)  # in place, seeded
+    assert (to_host(t) == (np.cumsum(x, dtype=np.uint32) + np.uint32(12345))).all()
+    f = rng.random(5 * tile + 9).astype(np.float32)
+    _check_scan(kf, oracle, f, "+", workgroup=workgroup, Nitem=nitem)
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", to_dev(x), workgroup=workgroup, Nitem=nitem)
+    for trial in range(4):  # a reused workspace: descriptors of the last call must not leak into the next
+        z = rng.integers(0, 1 << 32, n, dtype=np.uint32)
+        assert (to_host(kf.scan("+", to_dev(z), tmp=tmp, workgroup=workgroup, Nitem=nitem)) == np.cumsum(z, dtype=np.uint32)).all()
