@@ -330,3 +330,27 @@ def test_persistent_kernel_edges(kf, oracle, workgroup, nitem):
     for trial in range(4):  # a reused workspace: descriptors of the last call must not leak into the next
         z = rng.integers(0, 1 << 32, n, dtype=np.uint32)
         assert (to_host(kf.scan("+", to_dev(z), tmp=tmp, workgroup=workgroup, Nitem=nitem)) == np.cumsum(z, dtype=np.uint32)).all()
+
+
+def test_random_sizes_offsets_variants(kf, oracle):
+    """Many calls in a row with random lengths, view offsets, element widths and kernel variants,
+    in the spirit of the reference's repeated-trial loops (test/tests/scan/scan_test.jl:107-125)."""
+    import random
+
+    rnd = random.Random(11)
+    rng = np.random.default_rng(11)
+    pool = rng.integers(0, 1 << 31, (1 << 22) + 64, dtype=np.int64).astype(np.int32)
+    dev32 = to_dev(pool)
+    for it in range(60):
+        n = int(2 ** rnd.uniform(8, 22)) + rnd.randint(0, 5)
+        off = rnd.choice([0, 0, 1, 2, 3, 4])
+        var = rnd.choice([None, (768, 4), (640, 4), (512, 8), (256, 8)])
+        kw = {} if var is None else dict(workgroup=var[0], Nitem=var[1])
+        if rnd.random() < 0.5:
+            got = to_host(kf.scan("+", dev32[off:off + n], **kw))
+            assert (got == oracle.c_scan(0, 0, pool[off:off + n])).all(), (it, n, off, var)
+        else:
+            o2 = 2 * (off // 2)
+            h = pool[o2:o2 + 2 * (n // 2 + 1)].view(np.int64)
+            got = to_host(kf.scan("max", dev32[o2:o2 + 2 * (n // 2 + 1)].view(torch.int64), **kw))
+            assert (got == oracle.c_scan(0, 3, h)).all(), (it, n, off, var)
