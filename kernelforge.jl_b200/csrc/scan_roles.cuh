@@ -24,11 +24,13 @@
 //   resolvers (NRES warps; resolver q owns steps q, q + NRES, ...):
 //     1  when `totals[s]` completes: scan the warp totals (one shuffle scan), store the warps'
 //        exclusive prefixes, publish the tile AGGREGATE in the global descriptor array.
-//     2  once step s + LAG has been reduced (so that the predecessors have normally published): fold the
-//        predecessors' descriptors back to the nearest inclusive PREFIX, DEPTH coalesced rows of 32
-//        descriptors per round trip; publish the tile's inclusive PREFIX, store its exclusive
-//        prefix, arrive on `base[s]`. A window with a descriptor that is not yet published is
-//        simply read again; step 1 of later steps is never held up by that.
+//     2  once step s + LAG has been reduced (so that the predecessors have normally published): the
+//        step's exclusive prefix = the inclusive prefix of this resolver's PREVIOUS step combined with
+//        the AGGREGATES of the tiles in between (about NRES * gridDim.x of them), read DEPTH coalesced
+//        rows of 32 descriptors per round trip. Nobody's inclusive prefix is ever read from global
+//        memory, so resolving a tile depends on no other CTA having resolved anything. The resolver
+//        stores the exclusive prefix and arrives on `base[s]`. A window with a descriptor that is not
+//        yet published is simply read again; step 1 of later steps is never held up by that.
 //
 // Dependencies only ever point to smaller tile ids (tickets are handed out in order, every CTA is
 // resident, and reductions depend on nothing but loads), so the protocol cannot deadlock. Every
