@@ -9,7 +9,7 @@
 // the digit mask (`top_xor`); float keys add a shift and one logic op per key for the complement.
 //
 // Ranking matches digits across the warp (eight ballots per key): all lanes holding the same digit
-// find each other, the lowest such lane bumps the warp's private digit counter once for the whole group, and every lane
+// find each other, the highest such lane bumps the warp's private digit counter once for the whole group, and every lane
 // adds the count of lower lanes in its group. Ranks therefore follow element order for any data,
 // which is what makes each pass stable (shared-memory atomics alone would not guarantee it).
 //
@@ -61,14 +61,31 @@ template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT pad_key(
 // 32 mostly distinct values, the ballots are independent of each other and of other keys.
 __device__ __forceinline__ u32 match_digit(u32 d) {
     u32 peers = 0xFFFFFFFFu;
-#pragma unroll
-    for (int b = 0; b < 8; ++b) {
-        int mask;  // all ones when bit b of the digit is set, else zero
-        asm("bfe.s32 %0, %1, %2, 1;" : "=r"(mask) : "r"(d), "r"(b));
-        const u32 m = __ballot_sync(0xFFFFFFFFu, mask != 0);
-        peers &= ~(m ^ (u32)mask);  // lanes whose bit b equals mine: one three-input logic op
-    }
+    // Per digit bit: test it, ballot it, and keep the lanes whose bit equals mine: `peers & m` when my
+    // bit is set, `peers & ~m` (lop3 0x30) when it is clear, as two predicated instructions.
+#define KF_MATCH_BIT(BIT)                                                     \
+    asm("{\n .reg .pred p;\n .reg .b32 t, m;\n"                               \
+        " and.b32 t, %1, " #BIT ";\n setp.ne.u32 p, t, 0;\n"                   \
+        " vote.sync.ballot.b32 m, p, 0xffffffff;\n"                            \
+        " @p and.b32 %0, %0, m;\n @!p lop3.b32 %0, %0, m, 0, 0x30;\n}"         \
+        : "+r"(peers)                                                         \
+        : "r"(d));
+    KF_MATCH_BIT(1)
+    KF_MATCH_BIT(2)
+    KF_MATCH_BIT(4)
+    KF_MATCH_BIT(8)
+    KF_MATCH_BIT(16)
+    KF_MATCH_BIT(32)
+    KF_MATCH_BIT(64)
+    KF_MATCH_BIT(128)
+#undef KF_MATCH_BIT
     return peers;
+}
+// Highest set bit of a non-zero word (one instruction).
+__device__ __forceinline__ u32 highest_lane(u32 mask) {
+    u32 r;
+    asm("bfind.u32 %0, %1;" : "=r"(r) : "r"(mask));
+    return r;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -333,7 +350,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
             const u32 d = digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor);
             const u32 peers = match_digit(d);
             // lower lanes with my digit | leader lane << 8 | group size << 16
-            rank[i0 + i] = (u32)__popc(peers & lt) | ((u32)(__ffs(peers) - 1) << 8) | ((u32)__popc(peers) << 16);
+            rank[i0 + i] = (u32)__popc(peers & lt) | (highest_lane(peers) << 8) | ((u32)__popc(peers) << 16);
         }
 #pragma unroll
         for (int i = 0; i < BATCH; ++i) {
