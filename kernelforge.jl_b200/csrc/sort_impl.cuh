@@ -9,9 +9,10 @@
 // the digit mask (`top_xor`); float keys add a shift and one logic op per key for the complement.
 //
 // Ranking matches digits across the warp (eight ballots per key): all lanes holding the same digit
-// find each other, the highest such lane bumps the warp's private digit counter once for the whole group, and every lane
-// adds the count of lower lanes in its group. Ranks therefore follow element order for any data,
-// which is what makes each pass stable (shared-memory atomics alone would not guarantee it).
+// find each other, every lane reads the warp's private counter of the digit, the highest lane of the
+// group then bumps it once for the whole group, and every lane adds the count of lower lanes in its
+// group. Ranks therefore follow element order for any data, which is what makes each pass stable
+// (shared-memory atomics alone would not guarantee it).
 //
 // Tile descriptors are one 64-bit word per (tile, digit): {tag:8 | count:56}. The tag encodes the
 // pass and the state (aggregate / inclusive prefix / poison), so one descriptor array, cleared
@@ -336,33 +337,34 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
 
     KF_STRACE(1);
     // ---- 2. rank each key within (warp, digit), in element order --------------------------------
-    // Batches of BATCH keys: all match.any first, then the leaders' shared-memory atomics (issued in
-    // item order, which is what keeps equal digits in element order), then the broadcasts. The three
-    // steps of one key depend on each other, the keys of a batch do not, so their latencies overlap.
+    // Batches of BATCH keys: all digit matches first, then the counter reads and additions in item
+    // order (which is what keeps equal digits in element order). The keys of a batch do not depend
+    // on each other, so their latencies overlap.
     u32 rank[ITEMS];
     const u32 lt = lanemask_lt();
     constexpr int BATCH = ITEMS % 8 == 0 ? 8 : ITEMS;
 #pragma unroll
     for (int i0 = 0; i0 < ITEMS; i0 += BATCH) {
-        u32 before[BATCH];
+        u32 below[BATCH], size[BATCH], before[BATCH];
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {  // the matches of a batch are independent of each other
+            const u32 peers = match_digit(digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor));
+            below[i] = (u32)__popc(peers & lt);
+            size[i] = (u32)__popc(peers);
+        }
+        // In item order: every lane reads the warp's counter of its digit, then the last lane of each
+        // group adds the group's size to it. The counters are private to the warp and the warp's
+        // shared-memory accesses are performed in program order, so a later item sees the additions
+        // of the earlier ones and no value has to travel back from the adding lane.
 #pragma unroll
         for (int i = 0; i < BATCH; ++i) {
-            const u32 d = digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor);
-            const u32 peers = match_digit(d);
-            // lower lanes with my digit | leader lane << 8 | group size << 16
-            rank[i0 + i] = (u32)__popc(peers & lt) | (highest_lane(peers) << 8) | ((u32)__popc(peers) << 16);
+            u32 *slot = &my_hist[digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor)];
+            before[i] = *reinterpret_cast<volatile u32 *>(slot);
+            if (below[i] + 1u == size[i]) atomicAdd(slot, size[i]);
+            __syncwarp();
         }
 #pragma unroll
-        for (int i = 0; i < BATCH; ++i) {
-            const u32 d = digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor);
-            before[i] = 0;
-            if (((rank[i0 + i] >> 8) & 0xFFu) == lane) before[i] = atomicAdd(&my_hist[d], rank[i0 + i] >> 16);
-        }
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) {
-            const u32 b = __shfl_sync(0xFFFFFFFFu, before[i], (rank[i0 + i] >> 8) & 0xFFu);
-            rank[i0 + i] = b + (rank[i0 + i] & 0xFFu);
-        }
+        for (int i = 0; i < BATCH; ++i) rank[i0 + i] = before[i] + below[i];
     }
     __syncthreads();
     KF_STRACE(2);
