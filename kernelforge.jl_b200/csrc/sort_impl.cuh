@@ -495,7 +495,9 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         if (ok) {
             if (tile > 0) st_relaxed_u64(my_desc + lb_digit, tag_pfx | (excl + (u64)s_cnt[lb_digit]));
             // Global index of element idx of the sorted tile with digit d: gbase[d] + idx.
-            s_gbase[lb_digit] = a.gexcl[lb_digit] + excl - (u64)s_dexcl[lb_digit];
+            // keys only: the byte address of that element, so that the stream-out needs one multiply-add
+            const u64 g0 = a.gexcl[lb_digit] + excl - (u64)s_dexcl[lb_digit];
+            s_gbase[lb_digit] = SM::HAS_VAL ? g0 : (u64)(uintptr_t)kout + g0 * sizeof(KeyT);
         } else {
             st_relaxed_u64(my_desc + lb_digit, tag_poison);
             s_misc[10] = 1;
@@ -514,9 +516,13 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         if (full || idx < count) {
             const KeyT k = s_keys[idx];
             const u32 d = digit_of<KeyT, IS_FLOAT>(k, a.shift, a.top_xor);
-            const u64 o = s_gbase[d] + idx;
-            kout[o] = k;
-            if constexpr (SM::HAS_VAL) static_cast<ValS *>(a.vals_out)[o] = s_vals[idx];
+            if constexpr (SM::HAS_VAL) {
+                const u64 o = s_gbase[d] + idx;
+                kout[o] = k;
+                static_cast<ValS *>(a.vals_out)[o] = s_vals[idx];
+            } else {
+                *reinterpret_cast<KeyT *>(s_gbase[d] + (u64)idx * sizeof(KeyT)) = k;
+            }
         }
     }
     KF_STRACE(7);
