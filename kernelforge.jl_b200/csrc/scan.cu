@@ -92,7 +92,6 @@ extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t dtype, const void *src
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
     a.init = init;
     a.f = f;
-    a.block_order = cfg ? (cfg->reserved & 1) : 0;
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     switch (dtype) {
@@ -130,7 +129,6 @@ extern "C" int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, fl
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
     a.init = init_ab;
     a.f = KF_MAP_IDENTITY;
-    a.block_order = cfg ? (cfg->reserved & 1) : 0;
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     return scan_dispatch_affine_soa(p.variant, a_src, b_src, a_dst, b_dst, a, s);
@@ -155,7 +153,6 @@ extern "C" int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
     a.init = init_ab;
     a.f = KF_MAP_IDENTITY;
-    a.block_order = cfg ? (cfg->reserved & 1) : 0;
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     return scan_dispatch_affine_aos(p.variant, ab_src, ab_dst, a, s);

@@ -136,22 +136,8 @@ struct ScanArgs {
     const void *init;  // optional left seed (one element) or nullptr
     int vec_ok;     // all arrays share their 16-byte misalignment: full tiles use 128-bit accesses
     int f;
-    int block_order;  // experiment: tile id = blockIdx.x instead of an atomic ticket
-#ifdef KF_SCAN_TRACE
-    u64 *trace;       // lab builds only: 16 words per tile of phase timestamps
-#endif
 };
 
-#ifdef KF_SCAN_TRACE
-__device__ __forceinline__ u64 kf_now() {
-    u64 t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define KF_TRACE(slot, val) do { if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) args.trace[tile * 16 + (slot)] = (val); } while (0)
-#else
-#define KF_TRACE(slot, val) do { } while (0)
-#endif
 
 // Scans the VECS x EPV elements a thread holds (in place, inclusive within each slot) and the slot
 // totals across the warp. On return e[j][k] is inclusive within its slot, slot_excl[j] is the
@@ -451,15 +437,12 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
     const u32 tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
 
     if (tid == 0) {
-        s_tile = args.block_order ? (u64)blockIdx.x : (u64)atomicAdd(&args.header[kTicketBase], 1u);
+        s_tile = (u64)atomicAdd(&args.header[kTicketBase], 1u);
         s_abort = ld_relaxed_u32(&args.header[kStatusWord]) != 0u;
     }
     __syncthreads();
     const u64 tile = s_tile;
     if (tile >= args.ntiles) return;
-#ifdef KF_SCAN_TRACE
-    KF_TRACE(0, kf_now());
-#endif
     if (s_abort) {  // an earlier tile failed: pass the poison on so nobody waits for this tile
         if (tid == 0) Desc<T>::publish(args.desc, tile, kPoison, Op::template identity<T>());
         return;
@@ -502,9 +485,6 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
     const T carry = warp_tile_scan<T, Op, VECS, EPV>(e, slot_excl, lane);
     if (lane == 0) s_warp_total[warp] = carry;
     __syncthreads();
-#ifdef KF_SCAN_TRACE
-    KF_TRACE(1, kf_now());
-#endif
 
     // ---- warp prefix within the tile and the tile aggregate ----------------------------------
     T warp_excl = Op::template identity<T>();

@@ -245,21 +245,8 @@ struct SortPassArgs {
     int shift;
     u32 top_xor;
     int signed_or_float;
-#ifdef KF_SORT_TRACE
-    u64 *trace;  // lab builds only: 8 words per tile
-#endif
 };
 
-#ifdef KF_SORT_TRACE
-__device__ __forceinline__ u64 kf_sort_now() {
-    u64 t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define KF_STRACE(slot) do { if (threadIdx.x == 0) a.trace[tile * 8 + (slot)] = kf_sort_now(); } while (0)
-#else
-#define KF_STRACE(slot) do { } while (0)
-#endif
 
 template <typename KeyT, typename ValT, int THREADS, int ITEMS> struct SortSmem {
     static constexpr int WARPS = THREADS / 32;
@@ -314,7 +301,6 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         return;
     }
 
-    KF_STRACE(0);
     const u64 tile_start = tile * (u64)TILE;
     const u32 count = (u32)(a.n - tile_start < (u64)TILE ? a.n - tile_start : (u64)TILE);
     const bool full = count == (u32)TILE;
@@ -335,7 +321,6 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         }
     }
 
-    KF_STRACE(1);
     // ---- 2. rank each key within (warp, digit), in element order --------------------------------
     // Batches of BATCH keys: all digit matches first, then the counter reads and additions in item
     // order (which is what keeps equal digits in element order). The keys of a batch do not depend
@@ -367,7 +352,6 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         for (int i = 0; i < BATCH; ++i) rank[i0 + i] = before[i] + below[i];
     }
     __syncthreads();
-    KF_STRACE(2);
 
     // The look-back threads: one per digit. With 512 threads or more they are the second group of
     // 256 threads, which has nothing to do in steps 3 and 4, so the first round trip of the look-back
@@ -423,7 +407,6 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
     }
     __syncthreads();
 
-    KF_STRACE(3);
     // ---- 5. scatter keys (and values) to their sorted position in shared memory -----------------
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
@@ -448,7 +431,6 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         for (int i = 0; i < ITEMS; ++i) s_vals[rank[i]] = val[i];
     }
 
-    KF_STRACE(4);
     // ---- 6. look back: keys of my digit in all earlier tiles, LB tiles per round trip; the first
     //         round was read before the scatter ------------------------------------------------------
     if (is_lb) {
@@ -503,10 +485,8 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
             s_misc[10] = 1;
         }
     }
-    KF_STRACE(5);
     __syncthreads();
     if (s_misc[10]) return;
-    KF_STRACE(6);
 
     // ---- 7. stream the sorted tile out: consecutive threads write consecutive addresses within
     //         each digit's run ----------------------------------------------------------------
@@ -525,7 +505,6 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
             }
         }
     }
-    KF_STRACE(7);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
