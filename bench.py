@@ -100,6 +100,14 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # CPU arm (oracle/: the Base-like restatement)
 # ---------------------------------------------------------------------------------------------
+def host_threads():
+    """Host threads this process may use: its CPU affinity, not OMP_NUM_THREADS (torchrun sets that to 1)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_scan_sample(threads, n, repeats=3):
     """Times accumulate(+) over Float32 and UInt32 arrays of n elements; returns (GB/s, seconds per pass)."""
     import numpy as np
@@ -134,7 +142,7 @@ def run_reference_arm(args):
     if rank != 0:
         return 0
     from oracle import oracle as O
-    threads = O.max_threads()
+    threads = host_threads()
     n = 1 << 26
     for _ in range(args.warmup):
         cpu_scan_sample(threads, n, repeats=1)
@@ -587,7 +595,7 @@ def run_gpu_arm(args):
     line = None
     if rank == 0:
         from oracle import oracle as O
-        cpu = cpu_baseline_object(O.max_threads(), 1 << 26)
+        cpu = cpu_baseline_object(host_threads(), 1 << 26)
         prim = primitives_table(kf, torch, peak) if (args.detail and world == 1) else None
         line = {
             "metric": "effective GB/s, inclusive scan(+), Float32 + UInt32 at n=2^28 per GPU", "value": round(value, 1),
