@@ -547,7 +547,7 @@ def run_gpu_arm(args):
         b_ms = time_gpu(step, args.steps, torch)
         burst = {"value": round(step_bytes / (b_ms * 1e-3) / 1e9, 1), "ms_per_step": round(b_ms, 4),
                  "note": "the same K steps timed right after 0.5 s of idle (no power capping yet); `value` is timed inside the sustained window"}
-    roofline = {"bound": "hbm", "kernel": "scan_kernel_roles<uint32, +, 768x4, 2 buffers, reduction 3 tiles ahead>", "achieved": round(achieved, 1),
+    roofline = {"bound": "hbm", "kernel": "scan_kernel_roles<uint32, +, 384x8, 2 buffers, reduction 3 tiles ahead>", "achieved": round(achieved, 1),
                 "peak": peak, "peak_kind": peak_kind + " (STREAM-style copy)", "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                 "algorithmic_bytes_per_launch": 8 * n, "kernel_ms": round(kern_ms, 4), "traffic": traffic,

@@ -19,10 +19,11 @@ static const LaunchRow kLaunchTable[] = {
     {1, 0, 4194304ull, 256, 8, 0},
     {1, 8, 18446744073709551615ull, 512, 8, 0},
     {1, 2, 18446744073709551615ull, 512, 8, 0},
+    {1, 4, 18446744073709551615ull, 384, 8, 0},
     {1, 0, 18446744073709551615ull, 768, 4, 0},
     {2, 4, 18446744073709551615ull, 512, 24, 0},
     {2, 0, 18446744073709551615ull, 512, 16, 0},
     {3, 0, 18446744073709551615ull, 512, 16, 0},
 };
-static const int kNumLaunchRows = 10;
+static const int kNumLaunchRows = 11;
 }  // namespace kf

@@ -18,7 +18,7 @@ struct ScanVariant {
 static const ScanVariant kScanVariants[] = {
     {256, 4, false}, {512, 4, false}, {256, 8, false}, {128, 8, false},  // direct
     {768, 4, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead
-    {640, 4, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead
+    {384, 8, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead; fewest warps, holds its rate under the power cap
     {512, 8, true},                                                      // persistent: 2 buffers, reduction 3 tiles ahead (best for 2- and 8-byte elements)
 };
 constexpr int kNumScanVariants = 7;
@@ -68,7 +68,7 @@ int scan_launch(int variant, const Access &acc, const Arrays &arr, const ScanArg
     case 2: scan_kernel<T, Op, Access, 256, 8><<<grid, 256, 0, s>>>(acc, args); break;
     case 3: scan_kernel<T, Op, Access, 128, 8><<<grid, 128, 0, s>>>(acc, args); break;
     case 4: return scan_launch_ring_one<T, Op, Access, Arrays, 768, RV, 2, 3, 2>(acc, arr, args, s);
-    case 5: return scan_launch_ring_one<T, Op, Access, Arrays, 640, RV, 2, 3, 1>(acc, arr, args, s);
+    case 5: return scan_launch_ring_one<T, Op, Access, Arrays, 384, RV8, 2, 3, 2>(acc, arr, args, s);
     case 6: return scan_launch_ring_one<T, Op, Access, Arrays, 512, RV8, 2, 3, 2>(acc, arr, args, s);
     default: return KF_ERR_UNSUPPORTED;
     }

@@ -59,14 +59,14 @@ def main():
     print("| copy (torch, yardstick) | - | %.3f | %.0f |" % (ms, 8 * n / ms / 1e6))
     if "scan" in what:
         ws = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
-        for (t, v) in [(256, 4), (512, 4), (256, 8), (128, 8), (768, 4), (640, 4), (512, 8)]:
+        for (t, v) in [(256, 4), (512, 4), (256, 8), (128, 8), (768, 4), (384, 8), (512, 8)]:
             cfg = ctypes.pointer(C.LaunchCfg(t, v, 0, 0))
 
             def f():
                 rc = lib.kf_scan(0, 0, C.F32, xf.data_ptr(), out.data_ptr(), n, None, ws.data_ptr(), ws.numel(), cfg, st)
                 assert rc == 0, rc
             ms = timeit(f)
-            kind = "persistent" if (t >= 640 or (t, v) == (512, 8)) else "direct"
+            kind = "persistent" if (t, v) in ((768, 4), (384, 8), (512, 8)) else "direct"
             print("| scan f32 + | %s %dx%d | %.3f | %.0f |" % (kind, t, v, ms, 8 * n / ms / 1e6), flush=True)
         assert lib.kf_check(ws.data_ptr(), st) == 0
     if "sort" in what:

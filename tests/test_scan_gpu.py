@@ -96,9 +96,9 @@ def test_reused_tmp(kf, oracle, dtype, n):
         assert (to_host(dst) == np.cumsum(h, dtype=dtype)).all()  # small integers: exact in every type
 
 
-@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (256, 8), (128, 8), (768, 4), (640, 4), (512, 8)])
+@pytest.mark.parametrize("workgroup,nitem", [(256, 4), (512, 4), (256, 8), (128, 8), (768, 4), (384, 8), (512, 8)])
 def test_launch_variants(kf, oracle, workgroup, nitem):
-    """Every compiled variant: the direct kernels and the two persistent kernels (768, 640)."""
+    """Every compiled variant: the direct kernels and the persistent kernels (768x4, 384x8, 512x8)."""
     x = np.random.default_rng(2).integers(0, 256, 3_000_017).astype(np.uint32)
     _check_scan(kf, oracle, x, "+", workgroup=workgroup, Nitem=nitem)
     for dt in (np.uint8, np.float64):
@@ -299,7 +299,7 @@ def test_host_pipeline_chunk_ring(kf, oracle):
     assert (oc.numpy().astype(np.float64) == oracle.c_scan(0, 3, c)).all()
 
 
-@pytest.mark.parametrize("workgroup,nitem", [(768, 4), (640, 4), (512, 8)])
+@pytest.mark.parametrize("workgroup,nitem", [(768, 4), (384, 8), (512, 8)])
 def test_persistent_kernel_edges(kf, oracle, workgroup, nitem):
     """The persistent kernel forced onto sizes around its tile, ring and look-ahead boundaries: fewer
     tiles than ring steps, exactly one tile, one element over, fewer tiles than CTAs, a few more; a
@@ -344,7 +344,7 @@ def test_random_sizes_offsets_variants(kf, oracle):
     for it in range(60):
         n = int(2 ** rnd.uniform(8, 22)) + rnd.randint(0, 5)
         off = rnd.choice([0, 0, 1, 2, 3, 4])
-        var = rnd.choice([None, (768, 4), (640, 4), (512, 8), (256, 8)])
+        var = rnd.choice([None, (768, 4), (384, 8), (512, 8), (256, 8)])
         kw = {} if var is None else dict(workgroup=var[0], Nitem=var[1])
         if rnd.random() < 0.5:
             got = to_host(kf.scan("+", dev32[off:off + n], **kw))
