@@ -60,10 +60,7 @@ static int sort_plan(const KeyInfo &k, int val_bytes, u64 n, const kf_launch_cfg
     for (int i = 0; i < kNumSortVariants; ++i)
         if (kSortVariants[i].threads == t.threads && kSortVariants[i].items == t.items) v = i;
     if (v < 0) return KF_ERR_UNSUPPORTED;
-    // Shared memory of the variant: digit counters per warp + the staged tile.
-    const size_t smem = (size_t)(t.threads / 32) * kRadix * 4 + kRadix * 8 +
-                        (size_t)t.threads * t.items * (k.bytes + val_bytes) + 64;
-    if (smem > 227 * 1024) return KF_ERR_UNSUPPORTED;
+    if (sort_smem_bytes(t.threads, t.items, k.bytes, val_bytes) > 227 * 1024) return KF_ERR_UNSUPPORTED;
     p->variant = v;
     p->tile = (u64)t.threads * t.items;
     p->ntiles = (n + p->tile - 1) / p->tile;
@@ -109,7 +106,7 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
     default: rc = sort_hist_k64(k.is_float, keys_src, n, ghist, k.signed_or_float, s); break;
     }
     if (rc != KF_OK) return rc;
-    sort_scan_histogram_kernel<<<k.bytes, kRadix, 0, s>>>(ghist);
+    sort_scan_histogram_kernel<<<k.bytes, kRadix, 0, s>>>(ghist); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
 
     // Ping-pong plan: pass p writes dst when the number of passes still to come is even, else the
@@ -146,6 +143,8 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
         a.shift = 8 * pass;
         a.top_xor = (pass == P - 1 && k.signed_or_float) ? 0x80u : 0u;
         a.signed_or_float = k.signed_or_float;
+        a.spin_limit = test_spin_limit(cfg);
+        a.mute_tile = test_mute_tile(cfg);
         switch (k.bytes) {
         case 1: rc = sort_pass_k8(val_bytes, p.variant, a, s); break;
         case 2: rc = sort_pass_k16(val_bytes, p.variant, a, s); break;
@@ -221,6 +220,7 @@ extern "C" int32_t kf_iota(int32_t dtype, void *dst, uint64_t n, uint64_t start,
     if (dtype == KF_U32 || dtype == KF_I32) iota_kernel<uint32_t><<<(unsigned)blocks, 256, 0, s>>>((uint32_t *)dst, n, start);
     else if (dtype == KF_U64 || dtype == KF_I64) iota_kernel<u64><<<(unsigned)blocks, 256, 0, s>>>((u64 *)dst, n, start);
     else return KF_ERR_UNSUPPORTED;
+    note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }
@@ -233,6 +233,7 @@ static void launch_upper_bounds(const KeyInfo &k, const void *keys, u64 n, const
     else
         upper_bounds_kernel<KeyT, false><<<blocks, threads, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out,
                                                                      k.signed_or_float);
+    note_launch();
 }
 
 extern "C" int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t n, const void *splitters,
@@ -282,6 +283,7 @@ static void launch_bucket_ids(const KeyInfo &k, const void *keys, u64 n, const v
     else
         bucket_ids_kernel<KeyT, false><<<(unsigned)blocks, 256, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out,
                                                                          k.signed_or_float);
+    note_launch();
 }
 
 extern "C" int32_t kf_bucket_ids(int32_t key_dtype, const void *keys, uint64_t n, const void *splitters, int32_t nsplit,

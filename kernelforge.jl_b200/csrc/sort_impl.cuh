@@ -8,11 +8,16 @@
 // what moves. For integer keys the map only changes the top byte, so it costs one XOR folded into
 // the digit mask (`top_xor`); float keys add a shift and one logic op per key for the complement.
 //
-// Ranking matches digits across the warp (eight ballots per key): all lanes holding the same digit
-// find each other, every lane reads the warp's private counter of the digit, the highest lane of the
-// group then bumps it once for the whole group, and every lane adds the count of lower lanes in its
-// group. Ranks therefore follow element order for any data, which is what makes each pass stable
-// (shared-memory atomics alone would not guarantee it).
+// Ranking is done per half-warp ("unit" of 16 lanes, which owns 16 * ITEMS consecutive elements of
+// the tile) on a private table of one 32-bit word per digit: {lanes holding the digit in the
+// current item : 16 | keys of the digit seen in earlier items : 16}. Per item every lane announces
+// itself with an atomic add of its lane bit, the unit meets at a warp barrier, every lane reads the
+// word (its rank = count + number of lower lanes in the mask), the unit meets again, and the highest
+// lane of each group folds the group into the count with a second atomic add. Atomic adds commute
+// and the two warp barriers order them against the reads, so ranks follow element order for any
+// data on any schedule: that is what makes each pass stable (the reference leans on lane-ordered
+// resolution of same-address shared atomics, src/sort/onesweep_kernel.jl:19-24, which CUDA does
+// not promise).
 //
 // Tile descriptors are one 64-bit word per (tile, digit): {tag:8 | count:56}. The tag encodes the
 // pass and the state (aggregate / inclusive prefix / poison), so one descriptor array, cleared
@@ -44,10 +49,6 @@ template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT radix_bi
         return k;
     }
 }
-// `top_xor` is 0x80 on the most significant digit of signed and float keys, else 0.
-template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ u32 digit_of(KeyT k, int shift, u32 top_xor) {
-    return ((u32)(radix_bits<KeyT, IS_FLOAT>(k) >> shift) & 0xFFu) ^ top_xor;
-}
 // A key whose digit is 255 at every position (pads the last, ragged tile; it ranks after every
 // real key of the tile and is never written out).
 template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT pad_key(bool signed_or_float) {
@@ -55,38 +56,6 @@ template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ KeyT pad_key(
     // floats: a non-negative key keeps its bits -> the same pattern 0x7FFF...FF maps to all ones.
     KeyT all = (KeyT)~(KeyT)0;
     return signed_or_float ? (KeyT)(all >> 1) : all;
-}
-
-// Lanes of the warp that hold the same 8-bit digit as this one (its own bit included). Eight
-// ballots, one per digit bit: the hardware match.any instruction costs several hundred cycles on
-// 32 mostly distinct values, the ballots are independent of each other and of other keys.
-__device__ __forceinline__ u32 match_digit(u32 d) {
-    u32 peers = 0xFFFFFFFFu;
-    // Per digit bit: test it, ballot it, and keep the lanes whose bit equals mine: `peers & m` when my
-    // bit is set, `peers & ~m` (lop3 0x30) when it is clear, as two predicated instructions.
-#define KF_MATCH_BIT(BIT)                                                     \
-    asm("{\n .reg .pred p;\n .reg .b32 t, m;\n"                               \
-        " and.b32 t, %1, " #BIT ";\n setp.ne.u32 p, t, 0;\n"                   \
-        " vote.sync.ballot.b32 m, p, 0xffffffff;\n"                            \
-        " @p and.b32 %0, %0, m;\n @!p lop3.b32 %0, %0, m, 0, 0x30;\n}"         \
-        : "+r"(peers)                                                         \
-        : "r"(d));
-    KF_MATCH_BIT(1)
-    KF_MATCH_BIT(2)
-    KF_MATCH_BIT(4)
-    KF_MATCH_BIT(8)
-    KF_MATCH_BIT(16)
-    KF_MATCH_BIT(32)
-    KF_MATCH_BIT(64)
-    KF_MATCH_BIT(128)
-#undef KF_MATCH_BIT
-    return peers;
-}
-// Highest set bit of a non-zero word (one instruction).
-__device__ __forceinline__ u32 highest_lane(u32 mask) {
-    u32 r;
-    asm("bfind.u32 %0, %1;" : "=r"(r) : "r"(mask));
-    return r;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -245,40 +214,72 @@ struct SortPassArgs {
     int shift;
     u32 top_xor;
     int signed_or_float;
+    u32 spin_limit;    // polls before a look-back gives up
+    u32 mute_tile;     // test hook: 1 + index of a tile that publishes nothing (0 = none)
 };
 
+// Shared memory of one CTA: the per-unit digit tables, per-digit bases, the staged tile.
+__host__ __device__ constexpr size_t sort_smem_bytes(int threads, int items, int key_bytes, int val_bytes) {
+    return (size_t)(threads / 16) * kRadix * 4 + (size_t)kRadix * 16 + (size_t)threads * items * (key_bytes + val_bytes) + 64;
+}
 
 template <typename KeyT, typename ValT, int THREADS, int ITEMS> struct SortSmem {
-    static constexpr int WARPS = THREADS / 32;
+    static constexpr int UNITS = THREADS / 16;  // half-warps: the ranking units
     static constexpr int TILE = THREADS * ITEMS;
     static constexpr bool HAS_VAL = !std::is_same<ValT, void>::value;
     using ValS = typename std::conditional<HAS_VAL, ValT, char>::type;  // storage type (unused without values)
-    static constexpr size_t kWhist = (size_t)WARPS * kRadix * 4;
+    static constexpr size_t kTbl = (size_t)UNITS * kRadix * 4;
     static constexpr size_t kGbase = (size_t)kRadix * 16;  // global bases (u64) + digit counts + digit starts (u32)
     static constexpr size_t kKeys = (size_t)TILE * sizeof(KeyT);
     static constexpr size_t kVals = HAS_VAL ? (size_t)TILE * sizeof(ValS) : 0;
-    static constexpr size_t kBytes = kWhist + kGbase + kKeys + kVals + 64;
+    static constexpr size_t kBytes = sort_smem_bytes(THREADS, ITEMS, (int)sizeof(KeyT), HAS_VAL ? (int)sizeof(ValS) : 0);
+    static_assert(kBytes == kTbl + kGbase + kKeys + kVals + 64, "layout and size formula disagree");
 };
+
+// The byte of the key that this pass sorts by, BEFORE the sign flip of the top digit (`top_xor`):
+// per-key code works on this raw byte, and the per-digit code visits the table entries in the order
+// of the true digit (entry = digit ^ top_xor), which costs nothing per key.
+template <typename KeyT, bool IS_FLOAT> __device__ __forceinline__ u32 raw_digit(KeyT k, int shift) {
+    const KeyT b = radix_bits<KeyT, IS_FLOAT>(k);
+    if constexpr (sizeof(KeyT) == 8) return (u32)(b >> shift) & 0xFFu;
+    else return __byte_perm((u32)b, 0u, 0x4440u + (u32)(shift >> 3));  // one PRMT: byte `shift/8`, zero-extended
+}
+
+// Returns its argument through an empty asm statement: the compiler then recomputes what derives
+// from it (here: the table address of a key's digit) instead of keeping the first computation
+// alive in a register across the whole ranking step.
+template <typename KeyT> __device__ __forceinline__ KeyT opaque(KeyT k) {
+    if constexpr (sizeof(KeyT) == 8) {
+        asm volatile("" : "+l"(k));
+        return k;
+    } else {
+        u32 v = (u32)k;
+        asm volatile("" : "+r"(v));
+        return (KeyT)v;
+    }
+}
 
 template <typename KeyT, bool IS_FLOAT, typename ValT, int THREADS, int ITEMS>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512 ? 2 : 1))) onesweep_kernel(SortPassArgs a) {
     using SM = SortSmem<KeyT, ValT, THREADS, ITEMS>;
     using ValS = typename SM::ValS;
-    constexpr int WARPS = SM::WARPS;
+    constexpr int UNITS = SM::UNITS;
     constexpr int TILE = SM::TILE;
     static_assert(THREADS >= kRadix && THREADS % 32 == 0, "one thread per digit is required");
+    static_assert(TILE < 65536, "ranks and tile positions are kept in 16 bits");
 
     extern __shared__ __align__(16) unsigned char smem[];
-    u64 *s_gbase = reinterpret_cast<u64 *>(smem);                              // [256]
+    u64 *s_gbase = reinterpret_cast<u64 *>(smem);                              // [256] by table entry
     u32 *s_cnt = reinterpret_cast<u32 *>(smem + kRadix * 8);                   // [256] keys per digit (pads excluded)
     u32 *s_dexcl = s_cnt + kRadix;                                             // [256] start of each digit's run
-    u32 *s_whist = reinterpret_cast<u32 *>(smem + SM::kGbase);                 // [WARPS][256]
-    KeyT *s_keys = reinterpret_cast<KeyT *>(smem + SM::kGbase + SM::kWhist);   // [TILE]
-    ValS *s_vals = reinterpret_cast<ValS *>(smem + SM::kGbase + SM::kWhist + SM::kKeys);
-    u32 *s_misc = reinterpret_cast<u32 *>(smem + SM::kGbase + SM::kWhist + SM::kKeys + SM::kVals);
-    // s_misc[0..7]: warp sums of the digit scan; [8],[9]: tile ticket; [10]: abort flag
+    u32 *s_tbl = reinterpret_cast<u32 *>(smem + SM::kGbase);                   // [UNITS][256]
+    KeyT *s_keys = reinterpret_cast<KeyT *>(smem + SM::kGbase + SM::kTbl);     // [TILE]
+    ValS *s_vals = reinterpret_cast<ValS *>(smem + SM::kGbase + SM::kTbl + SM::kKeys);
+    u32 *s_misc = reinterpret_cast<u32 *>(smem + SM::kGbase + SM::kTbl + SM::kKeys + SM::kVals);
+    // s_misc[0..7]: warp sums of the digit scan; [8]: tile ticket; [10]: abort flag
 
     const u32 tid = threadIdx.x, lane = lane_id(), warp = tid >> 5;
+    const u32 hl = lane & 15u, unit = tid >> 4;
     const KeyT *kin = static_cast<const KeyT *>(a.keys_in);
     KeyT *kout = static_cast<KeyT *>(a.keys_out);
 
@@ -287,9 +288,11 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         s_misc[8] = t;
         s_misc[10] = ld_relaxed_u32(&a.header[kStatusWord]) != 0u;
     }
-    u32 *my_hist = s_whist + warp * kRadix;
+    {
+        uint4 *z = reinterpret_cast<uint4 *>(s_tbl);
 #pragma unroll
-    for (int i = 0; i < kRadix / 32; ++i) my_hist[i * 32 + lane] = 0;
+        for (int i = 0; i < UNITS * kRadix / 4 / THREADS; ++i) z[i * THREADS + tid] = make_uint4(0, 0, 0, 0);
+    }
     __syncthreads();
     const u64 tile = s_misc[8];
     if (tile >= a.ntiles) return;
@@ -300,56 +303,51 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         if (tid < kRadix) st_relaxed_u64(my_desc + tid, tag_poison);
         return;
     }
+    if (a.mute_tile && tile + 1 == (u64)a.mute_tile) return;  // test hook: a tile that never publishes
 
     const u64 tile_start = tile * (u64)TILE;
     const u32 count = (u32)(a.n - tile_start < (u64)TILE ? a.n - tile_start : (u64)TILE);
     const bool full = count == (u32)TILE;
-    const u32 warp_off = warp * 32 * ITEMS + lane;  // + i*32: element offset of item i in the tile
+    const u32 unit_off = unit * 16 * ITEMS + hl;  // + i*16: element offset of item i in the tile
 
-    // ---- 1. load keys (warp-striped: item i of lane l is element warp_off + 32*i) ---------------
+    // ---- 1. load keys (unit-striped: item i of lane hl of a unit is element unit_off + 16*i) -----
     KeyT key[ITEMS];
     if (full) {
-        const KeyT *p = kin + tile_start + warp_off;
+        const KeyT *p = kin + tile_start + unit_off;
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) key[i] = p[i * 32];
+        for (int i = 0; i < ITEMS; ++i) key[i] = p[i * 16];
     } else {
         const KeyT pad = pad_key<KeyT, IS_FLOAT>(a.signed_or_float != 0);
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
-            const u32 off = warp_off + i * 32;
+            const u32 off = unit_off + i * 16;
             key[i] = off < count ? kin[tile_start + off] : pad;
         }
     }
 
-    // ---- 2. rank each key within (warp, digit), in element order --------------------------------
-    // Batches of BATCH keys: all digit matches first, then the counter reads and additions in item
-    // order (which is what keeps equal digits in element order). The keys of a batch do not depend
-    // on each other, so their latencies overlap.
-    u32 rank[ITEMS];
-    const u32 lt = lanemask_lt();
-    constexpr int BATCH = ITEMS % 8 == 0 ? 8 : ITEMS;
+    // ---- 2. rank each key within (unit, digit), in element order ---------------------------------
+    // Word of the unit's table: {mask of the unit's lanes holding this digit in the current item : 16 |
+    // keys of this digit in the unit's earlier items : 16}. Per item: (A) add my lane bit; warp barrier;
+    // (B) read the word; warp barrier; (C) the highest lane of each group adds `group size - mask bits`.
+    // A, C are atomic adds, which commute, so a fast lane's A of the next item may overtake a slow
+    // group's C; every B sits between two warp barriers, after all A of its item and all C of the
+    // item before, and before any C of its own item: it reads exactly {group mask | earlier count}.
+    u32 *my_tbl = s_tbl + unit * kRadix;
+    const u32 bit_hi = 1u << (16 + hl);
+    const u32 lt16 = (1u << hl) - 1u;
+    u32 rank2[(ITEMS + 1) / 2];  // two 16-bit ranks (later: tile positions) per register
 #pragma unroll
-    for (int i0 = 0; i0 < ITEMS; i0 += BATCH) {
-        u32 below[BATCH], size[BATCH], before[BATCH];
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) {  // the matches of a batch are independent of each other
-            const u32 peers = match_digit(digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor));
-            below[i] = (u32)__popc(peers & lt);
-            size[i] = (u32)__popc(peers);
-        }
-        // In item order: every lane reads the warp's counter of its digit, then the last lane of each
-        // group adds the group's size to it. The counters are private to the warp and the warp's
-        // shared-memory accesses are performed in program order, so a later item sees the additions
-        // of the earlier ones and no value has to travel back from the adding lane.
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) {
-            u32 *slot = &my_hist[digit_of<KeyT, IS_FLOAT>(key[i0 + i], a.shift, a.top_xor)];
-            before[i] = *reinterpret_cast<volatile u32 *>(slot);
-            if (below[i] + 1u == size[i]) atomicAdd(slot, size[i]);
-            __syncwarp();
-        }
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) rank[i0 + i] = before[i] + below[i];
+    for (int i = 0; i < ITEMS; ++i) {
+        u32 *slot = my_tbl + raw_digit<KeyT, IS_FLOAT>(key[i], a.shift);
+        atomicAdd(slot, bit_hi);
+        __syncwarp();
+        const u32 w = *reinterpret_cast<volatile u32 *>(slot);
+        __syncwarp();
+        const u32 mask = w >> 16;
+        if ((mask >> hl) == 1u) atomicAdd(slot, (u32)__popc(mask) - (mask << 16));
+        const u32 r = (w & 0xFFFFu) + (u32)__popc(mask & lt16);
+        if (i & 1) rank2[i / 2] |= r << 16;
+        else rank2[i / 2] = r;
     }
     __syncthreads();
 
@@ -368,11 +366,13 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
     };
     if (LB_SPLIT && is_lb && tile > 0) lb_read((long long)tile - 1);
 
-    // ---- 3. per digit: count over the warps, publish the tile aggregate -------------------------
+    // ---- 3. per digit: count over the units, publish the tile aggregate -------------------------
+    // Thread `tid` owns the digit `tid` (in sorted order), whose table entry is tid ^ top_xor.
+    const u32 entry = (tid ^ a.top_xor) & 0xFFu;
     u32 cnt = 0;  // keys of digit `tid` in the tile, pads included
     if (tid < kRadix) {
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) cnt += s_whist[w * kRadix + tid];
+        for (int u = 0; u < UNITS; ++u) cnt += s_tbl[u * kRadix + entry];
         u32 cnt_real = cnt;  // pads excluded (they all have digit 255)
         if (!full && tid == kRadix - 1) cnt_real = cnt - ((u32)TILE - count);
         st_relaxed_u64(my_desc + tid, (tile == 0 ? tag_pfx : tag_agg) | (u64)cnt_real);
@@ -396,12 +396,12 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         for (int w = 0; w < kRadix / 32; ++w) wbase += w < (int)warp ? s_misc[w] : 0u;
         const u32 dexcl = wbase + incl - cnt;  // exclusive prefix of digit `tid` within the tile
         s_dexcl[tid] = dexcl;
-        // Turn the per-warp counts into the position of each (warp, digit) group in the sorted tile.
+        // Turn the per-unit counts into the position of each (unit, digit) group in the sorted tile.
         u32 run = dexcl;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
-            const u32 c = s_whist[w * kRadix + tid];
-            s_whist[w * kRadix + tid] = run;
+        for (int u = 0; u < UNITS; ++u) {
+            const u32 c = s_tbl[u * kRadix + entry];
+            s_tbl[u * kRadix + entry] = run;
             run += c;
         }
     }
@@ -410,25 +410,25 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
     // ---- 5. scatter keys (and values) to their sorted position in shared memory -----------------
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-        const u32 d = digit_of<KeyT, IS_FLOAT>(key[i], a.shift, a.top_xor);
-        rank[i] += my_hist[d];
-        s_keys[rank[i]] = key[i];
+        const u32 pos = my_tbl[raw_digit<KeyT, IS_FLOAT>(opaque(key[i]), a.shift)] + ((i & 1) ? rank2[i / 2] >> 16 : rank2[i / 2] & 0xFFFFu);
+        s_keys[pos] = key[i];
+        if constexpr (SM::HAS_VAL) rank2[i / 2] = (i & 1) ? (rank2[i / 2] & 0xFFFFu) | (pos << 16) : (rank2[i / 2] & 0xFFFF0000u) | pos;
     }
     if constexpr (SM::HAS_VAL) {
         const ValS *vin = static_cast<const ValS *>(a.vals_in);
         ValS val[ITEMS];
         if (full) {
 #pragma unroll
-            for (int i = 0; i < ITEMS; ++i) val[i] = (vin + tile_start + warp_off)[i * 32];
+            for (int i = 0; i < ITEMS; ++i) val[i] = (vin + tile_start + unit_off)[i * 16];
         } else {
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
-                const u32 off = warp_off + i * 32;
+                const u32 off = unit_off + i * 16;
                 val[i] = off < count ? vin[tile_start + off] : (ValS)0;
             }
         }
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) s_vals[rank[i]] = val[i];
+        for (int i = 0; i < ITEMS; ++i) s_vals[(i & 1) ? rank2[i / 2] >> 16 : rank2[i / 2] & 0xFFFFu] = val[i];
     }
 
     // ---- 6. look back: keys of my digit in all earlier tiles, LB tiles per round trip; the first
@@ -462,7 +462,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
                 if (done) break;
                 t -= used;  // tile 0 always publishes a prefix, so t never passes below -LB
                 if (used == 0) {
-                    if (++spins > kSpinLimit) {
+                    if (++spins > a.spin_limit) {
                         record_error(a.header, KF_ERR_TIMEOUT, (u32)tile);
                         ok = false;
                         break;
@@ -476,10 +476,10 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         }
         if (ok) {
             if (tile > 0) st_relaxed_u64(my_desc + lb_digit, tag_pfx | (excl + (u64)s_cnt[lb_digit]));
-            // Global index of element idx of the sorted tile with digit d: gbase[d] + idx.
+            // Global index of element idx of the sorted tile with digit d: gbase + idx.
             // keys only: the byte address of that element, so that the stream-out needs one multiply-add
             const u64 g0 = a.gexcl[lb_digit] + excl - (u64)s_dexcl[lb_digit];
-            s_gbase[lb_digit] = SM::HAS_VAL ? g0 : (u64)(uintptr_t)kout + g0 * sizeof(KeyT);
+            s_gbase[(lb_digit ^ a.top_xor) & 0xFFu] = SM::HAS_VAL ? g0 : (u64)(uintptr_t)kout + g0 * sizeof(KeyT);
         } else {
             st_relaxed_u64(my_desc + lb_digit, tag_poison);
             s_misc[10] = 1;
@@ -490,12 +490,14 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
 
     // ---- 7. stream the sorted tile out: consecutive threads write consecutive addresses within
     //         each digit's run ----------------------------------------------------------------
+    // (32-bit element bases instead of 64-bit ones were tried for n < 2^32: slower, the saved shared
+    // traffic is less than what the wider address arithmetic costs)
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const u32 idx = i * THREADS + tid;
         if (full || idx < count) {
             const KeyT k = s_keys[idx];
-            const u32 d = digit_of<KeyT, IS_FLOAT>(k, a.shift, a.top_xor);
+            const u32 d = raw_digit<KeyT, IS_FLOAT>(k, a.shift);
             if constexpr (SM::HAS_VAL) {
                 const u64 o = s_gbase[d] + idx;
                 kout[o] = k;
@@ -520,7 +522,7 @@ int onesweep_launch_one(const SortPassArgs &a, cudaStream_t s) {
     auto kern = onesweep_kernel<KeyT, IS_FLOAT, ValT, THREADS, ITEMS>;
     if (SM::kBytes > 227 * 1024) return KF_ERR_UNSUPPORTED;
     KF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes));
-    kern<<<(unsigned)a.ntiles, THREADS, SM::kBytes, s>>>(a);
+    kern<<<(unsigned)a.ntiles, THREADS, SM::kBytes, s>>>(a); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }
@@ -546,7 +548,7 @@ int histogram_launch(const void *keys, u64 n, u64 *ghist, int signed_or_float, c
         if (n * sizeof(KeyT) >= (8u << 20)) {
             auto kern = sort_histogram_lanes_kernel<KeyT, THREADS>;
             KF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
-            kern<<<(unsigned)sms, THREADS, kSmem, s>>>(static_cast<const KeyT *>(keys), n, ghist, signed_or_float, IS_FLOAT ? 1 : 0);
+            kern<<<(unsigned)sms, THREADS, kSmem, s>>>(static_cast<const KeyT *>(keys), n, ghist, signed_or_float, IS_FLOAT ? 1 : 0); note_launch();
             KF_CUDA_TRY(cudaGetLastError());
             return KF_OK;
         }
@@ -556,7 +558,7 @@ int histogram_launch(const void *keys, u64 n, u64 *ghist, int signed_or_float, c
     const u64 need = (n * sizeof(KeyT) + (u64)THREADS * 64 - 1) / ((u64)THREADS * 64);
     if (blocks > need) blocks = need < 1 ? 1 : need;
     sort_histogram_kernel<KeyT, IS_FLOAT, THREADS><<<(unsigned)blocks, THREADS, 0, s>>>(
-        static_cast<const KeyT *>(keys), n, ghist, signed_or_float);
+        static_cast<const KeyT *>(keys), n, ghist, signed_or_float); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }

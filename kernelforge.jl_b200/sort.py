@@ -36,7 +36,7 @@ def _reject(by, uint_map, lt, rev, algorithm):
 
 
 def sort_(*args, keys=None, keys_dst=None, by=None, uint_map=None, lt=None, rev=False, algorithm=None, tmp=None,
-          Nitem=None, Nchunks=None, workgroup=None, arch=None, family=None, rr=None):
+          Nitem=None, Nchunks=None, workgroup=None, arch=None, family=None, rr=None, _test_hook=0):
     """`sort!(src)` / `sort!(dst, src)`; with `keys=` the key-value form returning (dst, keys_dst)."""
     _reject(by, uint_map, lt, rev, algorithm)
     if len(args) == 1:
@@ -50,7 +50,7 @@ def sort_(*args, keys=None, keys_dst=None, by=None, uint_map=None, lt=None, rev=
     if dst.dtype != src.dtype or dst.numel() != src.numel():
         raise C.ArgumentError("dst and src must have the same element type and length")
     n = src.numel()
-    cfg = C.make_cfg(workgroup, Nitem, None)
+    cfg = C.make_cfg(workgroup, Nitem, None, _test_hook)
     lib = C.load()
     if keys is None:
         code = ops.dtype_code(src)

@@ -270,3 +270,68 @@ def test_full_size_2p28_pairs(kf):
     del m
     v = v_out.view(torch.int32)
     assert bool((v[1:][same] > v[:-1][same]).all().item())
+
+
+def test_bounded_wait_runs_out_in_a_sort_pass(kf, oracle):
+    """One tile of every pass publishes nothing: the look-back of the next tile gives up after its poll
+    limit, records KF_ERR_TIMEOUT and poisons its descriptors, later tiles return, the call returns.
+    The next sort on the same workspace is correct."""
+    from kernelforge_jl_b200 import _cabi as C
+    n = 30 * 512 * 24 + 5
+    x = rand_keys(np.uint32, n, np.random.default_rng(3))
+    src = to_dev(x)
+    dst = torch.empty_like(src)
+    tmp = kf.get_allocation(kf.Sort1D, src)
+    kf.sort_(dst, src, tmp=tmp, _test_hook=((1 + 2) << 16) | 300)
+    assert kf.lib.kf_check(tmp.ptr(), None) == C.ERR_TIMEOUT
+    header = tmp.workspace[:8].view(torch.int32).cpu().numpy()
+    assert header[0] == C.ERR_TIMEOUT and header[1] >= 2
+    kf.sort_(dst, src, tmp=tmp)
+    assert kf.lib.kf_check(tmp.ptr(), None) == C.OK
+    assert_same_bits(to_host(dst), oracle.c_sort(x))
+
+
+@pytest.mark.parametrize("seed", [3, 4])
+def test_random_stress_stability_every_variant(kf, oracle, seed):
+    """Seeded random cases (sizes 2^4..2^24, six key kinds including heavy duplicates, every compiled
+    launch variant): key-value sort with the original index as payload against the oracle's stable
+    permutation, and the keys-only sort, bit for bit. Restates the stability tests of the reference
+    (test/tests/sort/sort_test.jl:316-334) as a randomised sweep."""
+    import random
+    rnd = random.Random(seed)
+    rng = np.random.default_rng(seed)
+    for it in range(60):
+        n = int(2 ** rnd.uniform(4, 24)) + rnd.randint(0, 7)
+        kind = rnd.choice(["i32", "i64", "f32", "i16", "u8", "few", "few64"])
+        if kind == "i32":
+            k = rng.integers(-2**31, 2**31, n).astype(np.int32)
+        elif kind == "i64":
+            k = rng.integers(-2**62, 2**62, n).astype(np.int64)
+        elif kind == "f32":
+            k = rng.standard_normal(n).astype(np.float32)
+            k[::97] = -0.0
+        elif kind == "i16":
+            k = rng.integers(-2**15, 2**15, n).astype(np.int16)
+        elif kind == "u8":
+            k = rng.integers(0, 256, n).astype(np.uint8)
+        elif kind == "few":
+            k = rng.integers(0, 5, n).astype(np.int32)  # long groups of equal digits inside every half-warp
+        else:
+            k = (rng.integers(0, 3, n) * (1 << 40)).astype(np.int64)
+        var = rnd.choice([None, (512, 24), (512, 16), (384, 24), (256, 16)])
+        kw = {} if var is None else dict(workgroup=var[0], Nitem=var[1])
+        dk = to_dev(k)
+        idx = torch.arange(n, dtype=torch.int32, device="cuda")
+        vals, keys = kf.sort(idx, keys=dk, **kw)
+        perm = oracle.c_sortperm(k)
+        assert (to_host(vals).astype(np.uint64) == perm).all(), (it, n, kind, var)
+        assert_same_bits(to_host(keys), k[perm.astype(np.int64)])
+        assert_same_bits(to_host(kf.sort(dk, **kw)), k[perm.astype(np.int64)])
+
+
+@pytest.mark.parametrize("n,kind", [(30_000_001, "uint32"), (20_000_003, "float32"), (12_500_000, "int64")])
+def test_tens_of_millions_against_the_oracle(kf, oracle, n, kind):
+    """Thousands of tiles compared bit for bit with the oracle (the full-size tests check properties)."""
+    rng = np.random.default_rng(n)
+    x = rand_keys(np.dtype(kind).type, n, rng)
+    assert_same_bits(to_host(kf.sort(to_dev(x))), oracle.c_sort(x))
