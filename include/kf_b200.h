@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define KF_B200_ABI_VERSION 1
+#define KF_B200_ABI_VERSION 2
 
 /* CUDA stream handle (a `cudaStream_t` / `CUstream`); NULL = the legacy default stream. */
 typedef struct CUstream_st *kf_stream_t;
@@ -71,7 +71,7 @@ typedef enum kf_op {
     KF_OP_AFFINE = 7
 } kf_op;
 
-/* Post-map `g`: applied once to the final value (mapreduce). */
+/* Post-map `g`: applied once to the final value (mapreduce) and to every output element (scan). */
 typedef enum kf_post {
     KF_POST_IDENTITY = 0,
     KF_POST_SQRT = 1
@@ -98,7 +98,10 @@ typedef struct kf_launch_cfg {
     int32_t threads;
     int32_t items;
     int32_t blocks;
-    int32_t reserved;
+    int32_t reserved;  /* 0. Tests set it to make a bounded device-side wait run out on purpose: bits 0..15 =
+                        * polls before a look-back gives up (0 = the default, about a second), bits 16..31 =
+                        * 1 + index of one tile that stays silent. The call then returns normally and kf_check
+                        * reports KF_ERR_TIMEOUT; nothing faults or hangs. */
 } kf_launch_cfg;
 
 /* ---- library / errors ---------------------------------------------------------------------- */
@@ -122,6 +125,11 @@ int32_t kf_check(const void *ws, kf_stream_t stream);
 /* The launch table entry for (primitive, element size in bytes, n). Replaces the generated
  * `default_*` overrides loaded by src/tuning/loader.jl:93-130 from data/tuning/<Arch>_inline.jl. */
 int32_t kf_launch_table_lookup(int32_t primitive, int32_t elem_bytes, uint64_t n, kf_launch_cfg *out);
+
+/* Kernels this library has launched in the calling process so far (all threads, all devices; memsets
+ * and copies issued through the CUDA runtime are not kernels of the library and are not counted).
+ * A benchmark reads it before and after its timed region. It has no counterpart in the reference. */
+uint64_t kf_launch_count(void);
 
 /* Number of SMs of the current device. Replaces `num_sms` (ext/KernelForgeCUDAExt.jl:31-33). */
 int32_t kf_num_sms(void);
@@ -162,34 +170,38 @@ int32_t kf_mapreduce_multi(int32_t fn, int32_t op, int32_t g, int32_t dtype,
  * element type; pass KF_F32 with `pair = 1` for the affine (a, b) pair. */
 size_t kf_scan_workspace_bytes(int32_t dtype, int32_t pair, uint64_t n, const kf_launch_cfg *cfg);
 
-/* Inclusive scan: dst[i] = [init op] f(src[0]) op ... op f(src[i]). Single pass, decoupled
- * look-back over tile descriptors in the workspace; operand order is preserved.
- * `init` (device pointer to one element, may be NULL) is folded in from the left; it is how a
- * sharded scan seeds a shard with the carry of the shards before it.
+/* Inclusive scan: dst[i] = g([seed op] f(src[0]) op ... op f(src[i])). Single pass, decoupled
+ * look-back over tile descriptors in the workspace; operand order is preserved. `g` (a kf_post) is
+ * applied to every output element, never to the carried prefix (src/scan/scan_kernel.jl:463,470,474).
+ * `init` (device pointer to `ninit` elements, or NULL / 0) seeds the scan from the left with
+ * init[0] op ... op init[ninit-1]; a sharded scan passes the totals of all shards and ninit = its
+ * rank, so the carry of the shards before it needs no kernel of its own.
  * `dst == src` is allowed. n == 0 is a no-op (src/scan/scan.jl:273).
  * Replaces scan! / _scan_impl! (src/scan/scan.jl:261-284,414-479) and scan_kernel_packed! /
  * scan_kernel! (src/scan/scan_kernel.jl:310-478,94-299). */
-int32_t kf_scan(int32_t f, int32_t op, int32_t dtype,
-                const void *src, void *dst, uint64_t n, const void *init,
+int32_t kf_scan(int32_t f, int32_t op, int32_t g, int32_t dtype,
+                const void *src, void *dst, uint64_t n, const void *init, uint32_t ninit,
                 void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 
 /* Inclusive scan of affine maps x -> a*x + b under composition (KF_OP_AFFINE), Float32,
  * structure-of-arrays: (a_dst[i], b_dst[i]) = (a_0,b_0) o ... o (a_i,b_i). `init_ab` points to
- * two floats (a, b) or is NULL. In reference terms this is scan!(op, dst, src) over
- * NTuple{2,Float32} on the split-descriptor kernel (src/scan/scan_kernel.jl:94-299). */
+ * `ninit` interleaved (a, b) pairs that seed the scan from the left, or is NULL. In reference terms
+ * this is scan!(op, dst, src) over NTuple{2,Float32} on the split-descriptor kernel
+ * (src/scan/scan_kernel.jl:94-299). */
 int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, float *a_dst, float *b_dst,
-                           uint64_t n, const float *init_ab,
+                           uint64_t n, const float *init_ab, uint32_t ninit,
                            void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 
 /* Same, array-of-structures: src/dst hold n interleaved (a, b) pairs, i.e. the reference's
  * scan!(op, dst, src) over a Vector{NTuple{2,Float32}} (src/scan/scan.jl:261-284). */
-int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab,
+int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab, uint32_t ninit,
                            void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 
 /* Size of the fixed device array behind kf_scan_static: 1 MiB, held by every GPU that loads the
  * library until the process exits. It bounds the input: the call is refused when
- * kf_scan_workspace_bytes(dtype, 0, n, NULL) exceeds it (about 2^30 elements of up to 4 bytes,
- * 2^28 elements of 8 bytes). */
+ * kf_scan_workspace_bytes(dtype, 0, n, NULL) exceeds it. Largest n accepted, by element width
+ * (kf_scan_static_max_n computes it): 1 byte 4 293 885 952; 2 bytes 2 146 942 976;
+ * 4 bytes 1 073 471 488 (just under 2^30); 8 bytes 268 365 824 (just under 2^28). */
 #define KF_SCAN_STATIC_SCRATCH_BYTES (1u << 20)
 
 /* kf_scan for callers that cannot hand over a workspace because they cannot allocate device memory
@@ -199,19 +211,30 @@ int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const
  * that sits close to the device's memory limit where an allocation may fail or stall, and
  * latency-sensitive loops where cudaMalloc / cudaFree would synchronise the device.
  *
- * Same arguments, semantics and results as kf_scan with cfg == NULL, minus `ws`, `ws_bytes`, `cfg`.
- * The tile descriptors live in a fixed 1 MiB device array inside the library; the call itself
- * calls no cudaMalloc, cudaFree or allocating library routine.
+ * Same arguments, checks (in the same order), semantics and results as kf_scan with cfg == NULL,
+ * minus `ws`, `ws_bytes`, `cfg`. The tile descriptors live in a fixed 1 MiB device array inside the
+ * library; the call itself calls no cudaMalloc, cudaFree or allocating library routine.
  *   - The FIRST call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current) and caches it; make that first call before any stream capture.
  *   - All calls on one device share the array, and it keeps what the last call left there. Each call
  *     clears the part it uses first, so calls that follow one another on a stream are fine. Calls
  *     that overlap on the GPU (different streams, no ordering between them) race: do not do that.
- *   - Inputs whose descriptors do not fit return KF_ERR_EXCEEDS_STATIC_SCRATCH and touch nothing.
- *   - There is no workspace pointer to hand to kf_check; a device-side timeout shows as an output
- *     that was not written. */
-int32_t kf_scan_static(int32_t f, int32_t op, int32_t dtype,
-                       const void *src, void *dst, uint64_t n, const void *init, kf_stream_t stream);
+ *   - Inputs whose descriptors do not fit (n > kf_scan_static_max_n(dtype)) return
+ *     KF_ERR_EXCEEDS_STATIC_SCRATCH and touch nothing.
+ *   - kf_scan_static_check plays the part of kf_check: it reads the status word of the array. */
+int32_t kf_scan_static(int32_t f, int32_t op, int32_t g, int32_t dtype,
+                       const void *src, void *dst, uint64_t n, const void *init, uint32_t ninit,
+                       kf_stream_t stream);
+
+/* Largest n that kf_scan_static accepts for `dtype` (0 for an unknown dtype). No counterpart in the
+ * reference. */
+uint64_t kf_scan_static_max_n(int32_t dtype);
+
+/* kf_check for kf_scan_static: synchronises `stream` and returns the status word that the last
+ * kf_scan_static call on the current device left in the fixed array (KF_OK or KF_ERR_TIMEOUT).
+ * No counterpart in the reference, whose look-back spins are unbounded
+ * (src/scan/scan_kernel.jl:388-415). */
+int32_t kf_scan_static_check(kf_stream_t stream);
 
 /* ---- sort ---------------------------------------------------------------------------------- */
 

@@ -8,10 +8,12 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_int32, c_size_t, c_uint64, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_int32, c_size_t, c_uint32, c_uint64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libkf_b200.so")
+
+ABI_VERSION = 2  # KF_B200_ABI_VERSION of include/kf_b200.h
 
 # kf_status
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE_TOO_SMALL, ERR_LAUNCH_FAILED, ERR_TIMEOUT, ERR_EMPTY, \
@@ -48,6 +50,7 @@ PROTOTYPES = {
     "kf_last_cuda_error": (c_int32, []),
     "kf_check": (c_int32, [c_void_p, c_void_p]),
     "kf_launch_table_lookup": (c_int32, [c_int32, c_int32, c_uint64, POINTER(LaunchCfg)]),
+    "kf_launch_count": (c_uint64, []),
     "kf_num_sms": (c_int32, []),
     "kf_mapreduce_workspace_bytes": (c_size_t, [c_int32, c_uint64, POINTER(LaunchCfg)]),
     "kf_mapreduce": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_void_p, c_uint64, c_void_p,
@@ -55,12 +58,15 @@ PROTOTYPES = {
     "kf_mapreduce_multi": (c_int32, [c_int32, c_int32, c_int32, c_int32, POINTER(c_void_p), c_int32, c_uint64, c_void_p,
                                      c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_scan_workspace_bytes": (c_size_t, [c_int32, c_int32, c_uint64, POINTER(LaunchCfg)]),
-    "kf_scan": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_void_p, c_uint64, c_void_p,
+    "kf_scan": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_uint64, c_void_p, c_uint32,
                           c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
-    "kf_scan_static": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_void_p, c_uint64, c_void_p, c_void_p]),
-    "kf_scan_affine_soa": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_void_p,
+    "kf_scan_static": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_uint64, c_void_p, c_uint32,
+                                 c_void_p]),
+    "kf_scan_static_max_n": (c_uint64, [c_int32]),
+    "kf_scan_static_check": (c_int32, [c_void_p]),
+    "kf_scan_affine_soa": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint64, c_void_p, c_uint32,
                                      c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
-    "kf_scan_affine_aos": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p,
+    "kf_scan_affine_aos": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p, c_uint32,
                                      c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_sort_workspace_bytes": (c_size_t, [c_int32, c_int32, c_uint64, POINTER(LaunchCfg)]),
     "kf_sort_keys": (c_int32, [c_int32, c_void_p, c_void_p, c_uint64,
@@ -95,8 +101,8 @@ def load(path: str | None = None) -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
         fn.restype = res
         fn.argtypes = args
-    if lib.kf_abi_version() != 1:
-        raise KernelForgeError("libkf_b200.so has ABI version %d, expected 1" % lib.kf_abi_version())
+    if lib.kf_abi_version() != ABI_VERSION:
+        raise KernelForgeError("libkf_b200.so has ABI version %d, expected %d" % (lib.kf_abi_version(), ABI_VERSION))
     if path is None:
         _lib = lib
     return lib
@@ -118,8 +124,9 @@ def check(code: int, what: str) -> None:
     raise KernelForgeError(msg)
 
 
-def make_cfg(threads=None, items=None, blocks=None):
-    """A `kf_launch_cfg*` (or None) from the reference's `workgroup` / `Nitem` / `blocks` kwargs."""
-    if threads is None and items is None and blocks is None:
+def make_cfg(threads=None, items=None, blocks=None, reserved=0):
+    """A `kf_launch_cfg*` (or None) from the reference's `workgroup` / `Nitem` / `blocks` kwargs.
+    `reserved` is the test hook of kf_launch_cfg (spin limit and silent tile); 0 in production."""
+    if threads is None and items is None and blocks is None and not reserved:
         return None
-    return ctypes.pointer(LaunchCfg(int(threads or 0), int(items or 0), int(blocks or 0), 0))
+    return ctypes.pointer(LaunchCfg(int(threads or 0), int(items or 0), int(blocks or 0), int(reserved)))

@@ -4,9 +4,13 @@
 
 #include "launch_table.h"
 
+#include <atomic>
+
 namespace kf {
 
 static thread_local int g_last_cuda_error = 0;
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = (int)e; }
 
 // SM count of the current device; 148 (B200) when no device can be queried, so that size queries
@@ -51,6 +55,8 @@ extern "C" int32_t kf_check(const void *ws, kf_stream_t stream) {
     KF_CUDA_TRY(cudaStreamSynchronize(s));
     return (int32_t)status;
 }
+
+extern "C" uint64_t kf_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int32_t kf_num_sms(void) { return device_sm_count(); }
 

@@ -29,6 +29,15 @@ constexpr int kTicketBase = 8;
 // the limit is on the order of a second; a healthy look-back needs a handful of polls.
 constexpr u32 kSpinLimit = 1u << 20;
 
+// kf_launch_cfg.reserved is 0 in production. Tests use it to make a bounded wait run out without
+// faulting anything: bits 0..15 = polls before a wait gives up (0 = kSpinLimit), bits 16..31 = 1 + the
+// index of one tile that stays silent (publishes no descriptor and writes no output).
+inline u32 test_spin_limit(const kf_launch_cfg *cfg) {
+    const u32 v = cfg ? ((u32)cfg->reserved & 0xFFFFu) : 0u;
+    return v ? v : kSpinLimit;
+}
+inline u32 test_mute_tile(const kf_launch_cfg *cfg) { return cfg ? ((u32)cfg->reserved >> 16) : 0u; }
+
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // ---------------------------------------------------------------------------------------------
@@ -201,6 +210,15 @@ template <> __device__ __forceinline__ double apply_map<double>(int f, double x)
     return x;
 }
 
+// Post-map g (kf_post): applied once to the result of a mapreduce, and to every output element of a
+// scan (src/scan/scan_kernel.jl:463,470,474 of the reference).
+template <typename T> __device__ __forceinline__ T apply_post(int g, T x) {
+    if constexpr (IsFloat<T>::value) {
+        if (g == KF_POST_SQRT) return sqrt(x);  // IEEE round-to-nearest in the element type, like Julia's sqrt
+    }
+    return x;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Warp shuffles for any 4- or 8-byte trivially copyable type.
 // ---------------------------------------------------------------------------------------------
@@ -309,5 +327,8 @@ void set_last_cuda_error(cudaError_t e);
     } while (0)
 
 int device_sm_count();
+
+// Counts one kernel launch of this library (process-wide, read by kf_launch_count).
+void note_launch();
 
 }  // namespace kf

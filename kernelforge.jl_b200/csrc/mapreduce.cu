@@ -153,9 +153,9 @@ static int launch_mr(int variant, int blocks, const void *src, u64 n, void *dst,
     T *out = (T *)dst;
     T *part = (T *)partials;
     switch (variant) {
-    case 0: mapreduce_kernel<T, Op, 256, 4><<<blocks, 256, 0, s>>>(in, n, out, part, header, f, g); break;
-    case 1: mapreduce_kernel<T, Op, 512, 4><<<blocks, 512, 0, s>>>(in, n, out, part, header, f, g); break;
-    case 2: mapreduce_kernel<T, Op, 256, 8><<<blocks, 256, 0, s>>>(in, n, out, part, header, f, g); break;
+    case 0: mapreduce_kernel<T, Op, 256, 4><<<blocks, 256, 0, s>>>(in, n, out, part, header, f, g); note_launch(); break;
+    case 1: mapreduce_kernel<T, Op, 512, 4><<<blocks, 512, 0, s>>>(in, n, out, part, header, f, g); note_launch(); break;
+    case 2: mapreduce_kernel<T, Op, 256, 8><<<blocks, 256, 0, s>>>(in, n, out, part, header, f, g); note_launch(); break;
     default: return KF_ERR_UNSUPPORTED;
     }
     KF_CUDA_TRY(cudaGetLastError());

@@ -37,13 +37,6 @@ template <typename Op, typename T, int THREADS> __device__ __forceinline__ T blo
     return v;
 }
 
-template <typename T> __device__ __forceinline__ T apply_post(int g, T x) {
-    if constexpr (IsFloat<T>::value) {
-        if (g == KF_POST_SQRT) return (T)sqrt((double)x);
-    }
-    return x;
-}
-
 // Resolves the launch variant and the persistent grid size of a mapreduce call (mapreduce.cu).
 int mapreduce_resolve(int dtype, u64 n, const kf_launch_cfg *cfg, int *variant, int *blocks);
 

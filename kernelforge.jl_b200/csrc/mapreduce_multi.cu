@@ -128,7 +128,7 @@ static int launch_multi(int blocks, const void *const *srcs, u64 n, void *dst, v
     u64 head = mis ? (u64)(EPV - mis / sizeof(T)) : 0;
     if (head > n) head = n;
     mapreduce_multi_kernel<T, Op, NSRC, THREADS, UNROLL><<<blocks, THREADS, 0, s>>>(m, n, head, same ? 1 : 0, (T *)dst, (T *)partials,
-                                                                                   header, fn, g);
+                                                                                   header, fn, g); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }

@@ -69,13 +69,22 @@ extern "C" size_t kf_scan_workspace_bytes(int32_t dtype, int32_t pair, uint64_t 
     return scan_ws_bytes(p);
 }
 
-extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t dtype, const void *src, void *dst, uint64_t n,
-                           const void *init, void *ws, size_t ws_bytes, const kf_launch_cfg *cfg,
-                           kf_stream_t stream) {
-    const int eb = dtype_bytes(dtype);
-    if (eb == 0) return KF_ERR_INVALID_ARG;
+// Argument checks shared by kf_scan and kf_scan_static (everything that does not involve a workspace).
+static int scan_check_enums(int f, int op, int g, int dtype) {
+    if (dtype_bytes(dtype) == 0) return KF_ERR_INVALID_ARG;
     if (f < KF_MAP_IDENTITY || f > KF_MAP_ABS) return KF_ERR_UNSUPPORTED;
     if (op < KF_OP_ADD || op > KF_OP_XOR) return KF_ERR_UNSUPPORTED;
+    if (g < KF_POST_IDENTITY || g > KF_POST_SQRT) return KF_ERR_UNSUPPORTED;
+    if (g == KF_POST_SQRT && dtype != KF_F32 && dtype != KF_F64) return KF_ERR_UNSUPPORTED;
+    return KF_OK;
+}
+
+extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t g, int32_t dtype, const void *src, void *dst, uint64_t n,
+                           const void *init, uint32_t ninit, void *ws, size_t ws_bytes, const kf_launch_cfg *cfg,
+                           kf_stream_t stream) {
+    const int erc = scan_check_enums(f, op, g, dtype);
+    if (erc != KF_OK) return erc;
+    const int eb = dtype_bytes(dtype);
     if (n == 0) return KF_OK;
     if (!src || !dst || !ws) return KF_ERR_INVALID_ARG;
     if (((uintptr_t)src % eb) || ((uintptr_t)dst % eb) || ((uintptr_t)ws % 256) || (init && ((uintptr_t)init % eb)))
@@ -90,8 +99,12 @@ extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t dtype, const void *src
     scan_geometry(p, n, eb, 16 / eb, 1, ptrs, 2, &a);
     a.header = (u32 *)ws;
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
-    a.init = init;
+    a.init = ninit ? init : nullptr;
+    a.ninit = init ? ninit : 0;
     a.f = f;
+    a.g = g;
+    a.spin_limit = test_spin_limit(cfg);
+    a.mute_tile = test_mute_tile(cfg);
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     switch (dtype) {
@@ -110,7 +123,7 @@ extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t dtype, const void *src
 }
 
 extern "C" int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, float *a_dst, float *b_dst,
-                                      uint64_t n, const float *init_ab, void *ws, size_t ws_bytes,
+                                      uint64_t n, const float *init_ab, uint32_t ninit, void *ws, size_t ws_bytes,
                                       const kf_launch_cfg *cfg, kf_stream_t stream) {
     if (n == 0) return KF_OK;
     if (!a_src || !b_src || !a_dst || !b_dst || !ws) return KF_ERR_INVALID_ARG;
@@ -127,15 +140,19 @@ extern "C" int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, fl
     scan_geometry(p, n, 4, 4, 2, ptrs, 4, &a);
     a.header = (u32 *)ws;
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
-    a.init = init_ab;
+    a.init = ninit ? init_ab : nullptr;
+    a.ninit = init_ab ? ninit : 0;
     a.f = KF_MAP_IDENTITY;
+    a.g = KF_POST_IDENTITY;
+    a.spin_limit = test_spin_limit(cfg);
+    a.mute_tile = test_mute_tile(cfg);
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     return scan_dispatch_affine_soa(p.variant, a_src, b_src, a_dst, b_dst, a, s);
 }
 
 extern "C" int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab,
-                                      void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream) {
+                                      uint32_t ninit, void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream) {
     if (n == 0) return KF_OK;
     if (!ab_src || !ab_dst || !ws) return KF_ERR_INVALID_ARG;
     if (((uintptr_t)ab_src % 4) || ((uintptr_t)ab_dst % 4) || ((uintptr_t)ws % 256) ||
@@ -151,8 +168,12 @@ extern "C" int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64
     scan_geometry(p, n, 8, 2, 1, ptrs, 2, &a);
     a.header = (u32 *)ws;
     a.desc = (u64 *)((char *)ws + kHeaderBytes);
-    a.init = init_ab;
+    a.init = ninit ? init_ab : nullptr;
+    a.ninit = init_ab ? ninit : 0;
     a.f = KF_MAP_IDENTITY;
+    a.g = KF_POST_IDENTITY;
+    a.spin_limit = test_spin_limit(cfg);
+    a.mute_tile = test_mute_tile(cfg);
     cudaStream_t s = (cudaStream_t)stream;
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     return scan_dispatch_affine_aos(p.variant, ab_src, ab_dst, a, s);
@@ -187,17 +208,40 @@ int static_scratch(void **out) {
 }
 }  // namespace
 
-extern "C" int32_t kf_scan_static(int32_t f, int32_t op, int32_t dtype, const void *src, void *dst, uint64_t n,
-                                  const void *init, kf_stream_t stream) {
-    // Size first: a request beyond the fixed scratch is refused before anything touches the device.
-    const size_t need = kf_scan_workspace_bytes(dtype, 0, n, nullptr);
-    if (need == 0 && n != 0) return dtype_bytes(dtype) ? KF_ERR_UNSUPPORTED : KF_ERR_INVALID_ARG;
-    if (need > (size_t)KF_SCAN_STATIC_SCRATCH_BYTES) return KF_ERR_EXCEEDS_STATIC_SCRATCH;
+extern "C" uint64_t kf_scan_static_max_n(int32_t dtype) {
+    const int eb = dtype_bytes(dtype);
+    if (eb == 0) return 0;
+    // Largest n whose descriptors (sized like kf_scan_workspace_bytes does) fit the fixed array.
+    u64 lo = 0, hi = 1ull << 40;
+    while (lo < hi) {
+        const u64 mid = lo + (hi - lo + 1) / 2;
+        const size_t need = kf_scan_workspace_bytes(dtype, 0, mid, nullptr);
+        if (need != 0 && need <= (size_t)KF_SCAN_STATIC_SCRATCH_BYTES) lo = mid;
+        else hi = mid - 1;
+    }
+    return lo;
+}
+
+extern "C" int32_t kf_scan_static(int32_t f, int32_t op, int32_t g, int32_t dtype, const void *src, void *dst, uint64_t n,
+                                  const void *init, uint32_t ninit, kf_stream_t stream) {
+    // Same argument checks, in the same order, as kf_scan; then the size, so that a request beyond the
+    // fixed scratch is refused before anything touches the device.
+    const int erc = scan_check_enums(f, op, g, dtype);
+    if (erc != KF_OK) return erc;
     if (n == 0) return KF_OK;
+    const size_t need = kf_scan_workspace_bytes(dtype, 0, n, nullptr);
+    if (need == 0 || need > (size_t)KF_SCAN_STATIC_SCRATCH_BYTES) return KF_ERR_EXCEEDS_STATIC_SCRATCH;
     void *ws = nullptr;
     const int rc = static_scratch(&ws);
     if (rc != KF_OK) return rc;
     // kf_scan clears the header and the descriptors it is going to use at the start of the call, so
     // whatever the previous call left in the array does no harm.
-    return kf_scan(f, op, dtype, src, dst, n, init, ws, (size_t)KF_SCAN_STATIC_SCRATCH_BYTES, nullptr, stream);
+    return kf_scan(f, op, g, dtype, src, dst, n, init, ninit, ws, (size_t)KF_SCAN_STATIC_SCRATCH_BYTES, nullptr, stream);
+}
+
+extern "C" int32_t kf_scan_static_check(kf_stream_t stream) {
+    void *ws = nullptr;
+    const int rc = static_scratch(&ws);
+    if (rc != KF_OK) return rc;
+    return kf_check(ws, stream);
 }

@@ -133,10 +133,28 @@ struct ScanArgs {
     u64 ntiles;
     u64 *desc;      // Desc<T>::WORDS words per tile
     u32 *header;    // workspace header (status, ticket)
-    const void *init;  // optional left seed (one element) or nullptr
+    const void *init;  // optional left seed: `ninit` elements, folded left to right, or nullptr
     int vec_ok;     // all arrays share their 16-byte misalignment: full tiles use 128-bit accesses
     int f;
+    int g;          // kf_post applied to every output element (the carried prefix stays unmapped)
+    u32 ninit;
+    u32 spin_limit; // polls before a look-back gives up
+    u32 mute_tile;  // test hook: 1 + index of a tile that publishes nothing (0 = none)
 };
+
+template <typename T> __device__ __forceinline__ T post_elem(int g, T x) { return apply_post<T>(g, x); }
+template <> __device__ __forceinline__ Affine post_elem<Affine>(int, Affine x) { return x; }
+
+// The seed of the scan: init[0] op init[1] op ... (identity when there is none). A sharded scan passes
+// the totals of all shards and `ninit` = its rank, so the carry needs no kernel of its own.
+template <typename T, typename Op> __device__ __forceinline__ T fold_init(const ScanArgs &args) {
+    T acc = Op::template identity<T>();
+    if (args.init) {
+        const T *p = reinterpret_cast<const T *>(args.init);
+        for (u32 i = 0; i < args.ninit; ++i) acc = i == 0 ? p[0] : Op::template apply<T>(acc, p[i]);
+    }
+    return acc;
+}
 
 
 // Scans the VECS x EPV elements a thread holds (in place, inclusive within each slot) and the slot
@@ -171,108 +189,6 @@ __device__ __forceinline__ T warp_tile_scan(T (&e)[VECS][EPV], T (&slot_excl)[VE
         carry = Op::template apply<T>(carry, shfl_idx(incl[j], 31));
     }
     return carry;
-}
-
-// out[i] = in[(i + amount) mod N] for a lane-dependent amount, N a power of two: log2(N) stages of
-// selects, no dynamic register indexing.
-template <typename T, int N> __device__ __forceinline__ void rotate_regs(T (&x)[N], u32 amount) {
-#pragma unroll
-    for (int s = 1; s < N; s <<= 1) {
-        T y[N];
-        const bool on = (amount & s) != 0;
-#pragma unroll
-        for (int i = 0; i < N; ++i) y[i] = on ? x[(i + s) & (N - 1)] : x[i];
-#pragma unroll
-        for (int i = 0; i < N; ++i) x[i] = y[i];
-    }
-}
-
-// Blocked variant of the in-register tile scan, for data staged in shared memory. A thread owns
-// VECS CONSECUTIVE 16-byte slots (lane l of a warp: slots VECS*l .. VECS*l+VECS-1 of the warp's
-// run), so one warp scan covers VECS*EPV elements per thread instead of EPV. To keep the 128-bit
-// shared-memory accesses free of bank conflicts the thread touches its slots in a rotated order:
-// register j holds slot (j + rot) mod VECS, rot = blocked_rot(lane). On return r[j][k] is inclusive
-// within the WARP; the return value is the warp total (valid in every lane).
-template <int VECS> __device__ __forceinline__ u32 blocked_rot(u32 lane) {
-    static_assert(VECS == 2 || VECS == 4 || VECS == 8, "rotation scheme covers 2, 4 and 8 slots per thread");
-    return (lane >> (VECS == 8 ? 0 : (VECS == 4 ? 1 : 2))) & (VECS - 1);
-}
-template <typename T, typename Op, int VECS, int EPV>
-__device__ __forceinline__ T warp_tile_scan_blocked(T (&r)[VECS][EPV], u32 rot, u32 lane) {
-    T tot[VECS];
-#pragma unroll
-    for (int j = 0; j < VECS; ++j) {
-#pragma unroll
-        for (int k = 1; k < EPV; ++k) r[j][k] = Op::template apply<T>(r[j][k - 1], r[j][k]);
-        tot[j] = r[j][EPV - 1];
-    }
-    rotate_regs<T, VECS>(tot, (VECS - rot) & (VECS - 1));  // tot[m]: total of the thread's m-th slot
-    T excl[VECS];
-    excl[0] = Op::template identity<T>();
-#pragma unroll
-    for (int m = 1; m < VECS; ++m) excl[m] = Op::template apply<T>(excl[m - 1], tot[m - 1]);
-    const T thread_total = Op::template apply<T>(excl[VECS - 1], tot[VECS - 1]);
-    T incl = thread_total;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        T up = shfl_up(incl, d);
-        up = lane >= (u32)d ? up : Op::template identity<T>();
-        incl = Op::template apply<T>(up, incl);
-    }
-    T before = shfl_up(incl, 1);
-    before = lane == 0 ? Op::template identity<T>() : before;
-    rotate_regs<T, VECS>(excl, rot);  // excl[j]: prefix of the slot register j holds
-#pragma unroll
-    for (int j = 0; j < VECS; ++j) {
-        const T p = Op::template apply<T>(before, excl[j]);
-#pragma unroll
-        for (int k = 0; k < EPV; ++k) r[j][k] = Op::template apply<T>(p, r[j][k]);
-    }
-    return shfl_idx(incl, 31);
-}
-
-// Striped in-register tile scan whose cross-lane step goes through a small per-warp scratch in
-// shared memory: the VECS*32 slot totals of a warp are written in element order (v, lane), each
-// lane then takes VECS CONSECUTIVE totals, scans them sequentially, ONE warp scan combines the 32
-// lane sums, and the exclusive prefixes travel back the same way. Same result as warp_tile_scan
-// (e[v][k] inclusive within the warp afterwards, not only within the slot) for about a third of
-// the instructions, and the registers stay striped, so global stores stay coalesced.
-// `scratch` holds VECS*32 elements of T per warp. Returns the warp total (valid in every lane).
-template <typename T, typename Op, int VECS, int EPV>
-__device__ __forceinline__ T warp_tile_scan_via_smem(T (&e)[VECS][EPV], T *scratch, u32 lane) {
-#pragma unroll
-    for (int v = 0; v < VECS; ++v) {
-#pragma unroll
-        for (int k = 1; k < EPV; ++k) e[v][k] = Op::template apply<T>(e[v][k - 1], e[v][k]);
-        scratch[v * 32 + lane] = e[v][EPV - 1];
-    }
-    __syncwarp();
-    T c[VECS];
-#pragma unroll
-    for (int i = 0; i < VECS; ++i) c[i] = scratch[lane * VECS + i];
-#pragma unroll
-    for (int i = 1; i < VECS; ++i) c[i] = Op::template apply<T>(c[i - 1], c[i]);
-    T incl = c[VECS - 1];
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        T up = shfl_up(incl, d);
-        up = lane >= (u32)d ? up : Op::template identity<T>();
-        incl = Op::template apply<T>(up, incl);
-    }
-    T before = shfl_up(incl, 1);
-    before = lane == 0 ? Op::template identity<T>() : before;
-    scratch[lane * VECS] = before;
-#pragma unroll
-    for (int i = 1; i < VECS; ++i) scratch[lane * VECS + i] = Op::template apply<T>(before, c[i - 1]);
-    __syncwarp();
-#pragma unroll
-    for (int v = 0; v < VECS; ++v) {
-        const T p = scratch[v * 32 + lane];
-#pragma unroll
-        for (int k = 0; k < EPV; ++k) e[v][k] = Op::template apply<T>(p, e[v][k]);
-    }
-    __syncwarp();  // the scratch may be reused right away
-    return shfl_idx(incl, 31);
 }
 
 // CTA-wide barrier, or a named barrier over the first BAR_THREADS threads when part of the CTA
@@ -373,8 +289,7 @@ __device__ __forceinline__ bool resolve_tile_prefix_block(const ScanArgs &args, 
                                                           int *s_abort, u32 *s_info, T *s_val, T &excl_out) {
     const u32 tid = threadIdx.x;
     if (tile == 0) {
-        T excl = Op::template identity<T>();
-        if (args.init) excl = *reinterpret_cast<const T *>(args.init);
+        const T excl = fold_init<T, Op>(args);
         if (tid == 0) Desc<T>::publish(args.desc, tile, kPrefix, Op::template apply<T>(excl, tile_total));
         excl_out = excl;
         return true;
@@ -400,7 +315,7 @@ __device__ __forceinline__ bool resolve_tile_prefix_block(const ScanArgs &args, 
             base -= 32 * WARPS;  // nothing but aggregates in sight: keep walking back
             spins = 0;
         } else {
-            if (++spins > kSpinLimit) {
+            if (++spins > args.spin_limit) {
                 timed_out = true;
                 how = 2;
                 break;
@@ -447,6 +362,7 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
         if (tid == 0) Desc<T>::publish(args.desc, tile, kPoison, Op::template identity<T>());
         return;
     }
+    if (args.mute_tile && tile + 1 == (u64)args.mute_tile) return;  // test hook: a tile that never publishes
 
     // Tile extent. With a misaligned base, tile 0 is the short scalar head.
     const u64 first = args.head > 0 ? 1 : 0;
@@ -501,26 +417,38 @@ __global__ void __launch_bounds__(THREADS) scan_kernel(Access acc, ScanArgs args
     if (!resolve_tile_prefix_block<T, Op, WARPS, true, 0>(args, tile, tile_total, warp, lane, &s_abort, s_lb_info, s_lb_val, tile_excl)) return;
 
     // ---- apply the prefix and store -----------------------------------------------------------
+    // (the post-map g is a uniform switch around the whole store loop, so that the common g = identity
+    // path carries no per-element branch)
     const T base = Op::template apply<T>(tile_excl, warp_excl);
-    if (fast) {
+    auto emit = [&](auto with_g) {
+        constexpr bool WITH_G = decltype(with_g)::value;
+        if (fast) {
 #pragma unroll
-        for (int j = 0; j < VECS; ++j) {
-            const T p = Op::template apply<T>(base, slot_excl[j]);
+            for (int j = 0; j < VECS; ++j) {
+                const T p = Op::template apply<T>(base, slot_excl[j]);
 #pragma unroll
-            for (int k = 0; k < EPV; ++k) e[j][k] = Op::template apply<T>(p, e[j][k]);
-            acc.store_slot(start + (warp_slot0 + (u64)j * 32 + lane) * EPV, e[j]);
-        }
-    } else {
+                for (int k = 0; k < EPV; ++k) {
+                    e[j][k] = Op::template apply<T>(p, e[j][k]);
+                    if constexpr (WITH_G) e[j][k] = post_elem<T>(args.g, e[j][k]);
+                }
+                acc.store_slot(start + (warp_slot0 + (u64)j * 32 + lane) * EPV, e[j]);
+            }
+        } else {
 #pragma unroll
-        for (int j = 0; j < VECS; ++j) {
-            const T p = Op::template apply<T>(base, slot_excl[j]);
+            for (int j = 0; j < VECS; ++j) {
+                const T p = Op::template apply<T>(base, slot_excl[j]);
 #pragma unroll
-            for (int k = 0; k < EPV; ++k) {
-                const u64 off = (warp_slot0 + (u64)j * 32 + lane) * EPV + k;
-                if (off < count) acc.store_elem(start + off, Op::template apply<T>(p, e[j][k]));
+                for (int k = 0; k < EPV; ++k) {
+                    const u64 off = (warp_slot0 + (u64)j * 32 + lane) * EPV + k;
+                    T v = Op::template apply<T>(p, e[j][k]);
+                    if constexpr (WITH_G) v = post_elem<T>(args.g, v);
+                    if (off < count) acc.store_elem(start + off, v);
+                }
             }
         }
-    }
+    };
+    if (args.g == KF_POST_IDENTITY) emit(std::false_type{});
+    else emit(std::true_type{});
 }
 
 }  // namespace kf

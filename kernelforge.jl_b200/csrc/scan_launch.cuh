@@ -52,7 +52,7 @@ int scan_launch_ring_one(const Access &acc, const Arrays &arr, const ScanArgs &a
     // One CTA per SM: the look-ahead distance K is tuned for tiles of that size arriving at that rate.
     u64 grid = (u64)device_sm_count();
     if (grid > args.ntiles) grid = args.ntiles;
-    kern<<<(unsigned)grid, CTA, SM::kBytes, s>>>(acc, arr, args);
+    kern<<<(unsigned)grid, CTA, SM::kBytes, s>>>(acc, arr, args); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }
@@ -63,12 +63,16 @@ int scan_launch(int variant, const Access &acc, const Arrays &arr, const ScanArg
     constexpr int RV = 4 / Arrays::NARR;   // ring vectors per thread and array
     constexpr int RV8 = 8 / Arrays::NARR;
     switch (variant) {
-    case 0: scan_kernel<T, Op, Access, 256, 4><<<grid, 256, 0, s>>>(acc, args); break;
-    case 1: scan_kernel<T, Op, Access, 512, 4><<<grid, 512, 0, s>>>(acc, args); break;
-    case 2: scan_kernel<T, Op, Access, 256, 8><<<grid, 256, 0, s>>>(acc, args); break;
-    case 3: scan_kernel<T, Op, Access, 128, 8><<<grid, 128, 0, s>>>(acc, args); break;
+    case 0: scan_kernel<T, Op, Access, 256, 4><<<grid, 256, 0, s>>>(acc, args); note_launch(); break;
+    case 1: scan_kernel<T, Op, Access, 512, 4><<<grid, 512, 0, s>>>(acc, args); note_launch(); break;
+    case 2: scan_kernel<T, Op, Access, 256, 8><<<grid, 256, 0, s>>>(acc, args); note_launch(); break;
+    case 3: scan_kernel<T, Op, Access, 128, 8><<<grid, 128, 0, s>>>(acc, args); note_launch(); break;
     case 4: return scan_launch_ring_one<T, Op, Access, Arrays, 768, RV, 2, 3, 2>(acc, arr, args, s);
     case 5: return scan_launch_ring_one<T, Op, Access, Arrays, 384, RV8, 2, 3, 2>(acc, arr, args, s);
+    // 8-byte elements and affine pairs (64 KB tiles) read 1.25 x their input from DRAM in this variant:
+    // three tiles per SM between reduction and scan, plus the output written in between, overflow what
+    // L2 keeps. Both cures were measured and are slower: reducing two tiles ahead (reads back to 1.05 x,
+    // but the descriptor latency shows) and 48 KB tiles (512 x 6 vectors).
     case 6: return scan_launch_ring_one<T, Op, Access, Arrays, 512, RV8, 2, 3, 2>(acc, arr, args, s);
     default: return KF_ERR_UNSUPPORTED;
     }

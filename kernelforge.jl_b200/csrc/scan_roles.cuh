@@ -261,7 +261,8 @@ __global__ void __launch_bounds__(THREADS + 32 + 32 * NRES) scan_kernel_roles(Ac
                         const T total = shfl_idx(incl, 31);
                         if (lane == 0) {
                             slot_ref(&s_tile_total[q]) = total;
-                            Desc<T>::publish(args.desc, tile, kAggregate, total);
+                            // (test hook: a muted tile keeps its aggregate to itself)
+                            if (!(args.mute_tile && tile + 1 == (u64)args.mute_tile)) Desc<T>::publish(args.desc, tile, kAggregate, total);
                         }
                         j += NRES;
                         idle = 0;
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(THREADS + 32 + 32 * NRES) scan_kernel_roles(Ac
                         ok = false;
                     } else if (missing) {  // a predecessor has not published yet: come back
                         ++spins;
-                        if (spins > kSpinLimit) {
+                        if (spins > args.spin_limit) {
                             if (lane == 0) wait_failed((u32)R);
                             ok = false;
                         } else if ((spins & 15) == 15 && *reinterpret_cast<volatile int *>(s_abort)) {
@@ -341,7 +342,7 @@ __global__ void __launch_bounds__(THREADS + 32 + 32 * NRES) scan_kernel_roles(Ac
                 if (resolved) {
                     T excl = acc_r;
                     if (have_prev) excl = Op::template apply<T>(prev_incl, acc_r);
-                    else if (args.init) excl = Op::template apply<T>(*reinterpret_cast<const T *>(args.init), acc_r);
+                    else if (args.init && args.ninit) excl = Op::template apply<T>(fold_init<T, Op>(args), acc_r);
                     prev_incl = Op::template apply<T>(excl, slot_ref(&s_tile_total[rq]));
                     prev_tile = (long long)R;
                     have_prev = true;
@@ -483,25 +484,35 @@ __global__ void __launch_bounds__(THREADS + 32 + 32 * NRES) scan_kernel_roles(Ac
                 break;
             }
             const T base = Op::template apply<T>(slot_ref(&s_tile_excl[q]), slot_ref(&s_warp_excl[q * WARPS + warp]));
+            // (the post-map g is a uniform switch around the whole store loop: g = identity carries no
+            // per-element branch)
+            auto emit = [&](auto with_g) {
+                constexpr bool WITH_G = decltype(with_g)::value;
 #pragma unroll
-            for (int v = 0; v < VECS; ++v) {
-                const T p = Op::template apply<T>(base, slot_excl[v]);
-#pragma unroll
-                for (int k = 0; k < EPV; ++k) e[v][k] = Op::template apply<T>(p, e[v][k]);
-                if (fast) {
-                    uint4 raw[NARR];
-                    Arrays::pack(e[v], raw);
-#pragma unroll
-                    for (int a = 0; a < NARR; ++a)
-                        st_stream_v4(arr.dst[a] + start * Arrays::elem_bytes + (size_t)(warp_slot0 + v * 32 + lane) * 16, raw[a]);
-                } else {
+                for (int v = 0; v < VECS; ++v) {
+                    const T p = Op::template apply<T>(base, slot_excl[v]);
 #pragma unroll
                     for (int k = 0; k < EPV; ++k) {
-                        const u64 off = (u64)(warp_slot0 + v * 32 + lane) * EPV + k;
-                        if (off < count) acc.store_elem(start + off, e[v][k]);
+                        e[v][k] = Op::template apply<T>(p, e[v][k]);
+                        if constexpr (WITH_G) e[v][k] = post_elem<T>(args.g, e[v][k]);
+                    }
+                    if (fast) {
+                        uint4 raw[NARR];
+                        Arrays::pack(e[v], raw);
+#pragma unroll
+                        for (int a = 0; a < NARR; ++a)
+                            st_stream_v4(arr.dst[a] + start * Arrays::elem_bytes + (size_t)(warp_slot0 + v * 32 + lane) * 16, raw[a]);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < EPV; ++k) {
+                            const u64 off = (u64)(warp_slot0 + v * 32 + lane) * EPV + k;
+                            if (off < count) acc.store_elem(start + off, e[v][k]);
+                        }
                     }
                 }
-            }
+            };
+            if (args.g == KF_POST_IDENTITY) emit(std::false_type{});
+            else emit(std::true_type{});
         }
     }
 

@@ -40,17 +40,6 @@ __device__ __forceinline__ void bulk_load(void *dst_smem, const void *src_gmem, 
                  "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
                  : "memory");
 }
-// shared -> global bulk copy, tracked by the thread's bulk async-group.
-__device__ __forceinline__ void bulk_store(void *dst_gmem, const void *src_smem, u32 bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_addr(src_smem)),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void bulk_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Array views for the bulk path: NARR arrays, each contributing one 16-byte vector per slot.

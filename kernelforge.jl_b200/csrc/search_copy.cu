@@ -244,6 +244,7 @@ static int launch_argmax(bool greater, int blocks, const void *src, u64 n, void 
                          cudaStream_t s) {
     if (greater) argmax_kernel<T, true, 256, 4><<<blocks, 256, 0, s>>>((const T *)src, n, (T *)ov, oi, (T *)pv, pi, header, f);
     else argmax_kernel<T, false, 256, 4><<<blocks, 256, 0, s>>>((const T *)src, n, (T *)ov, oi, (T *)pv, pi, header, f);
+    note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }
@@ -256,7 +257,7 @@ static int launch_find(const void *src, u64 n, int pred, const void *operand, in
     const u64 nchunks = (n + (u64)THREADS * ITEMS - 1) / ((u64)THREADS * ITEMS);
     u64 blocks = (u64)device_sm_count() * 8;
     if (blocks > nchunks) blocks = nchunks;
-    find_kernel<T, THREADS, ITEMS><<<(unsigned)blocks, THREADS, 0, s>>>((const T *)src, n, pred, y, last, result);
+    find_kernel<T, THREADS, ITEMS><<<(unsigned)blocks, THREADS, 0, s>>>((const T *)src, n, pred, y, last, result); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }
@@ -338,9 +339,9 @@ extern "C" int32_t kf_vcopy(void *dst, const void *src, uint64_t nbytes, kf_stre
     if (ms == md) {
         u64 head = ms ? 16 - ms : 0;
         if (head > nbytes) head = nbytes;
-        vcopy_kernel<256, 4><<<stream_grid(nbytes, 256, 4), 256, 0, s>>>((const unsigned char *)src, (unsigned char *)dst, nbytes, head);
+        vcopy_kernel<256, 4><<<stream_grid(nbytes, 256, 4), 256, 0, s>>>((const unsigned char *)src, (unsigned char *)dst, nbytes, head); note_launch();
     } else {
-        bcopy_kernel<<<device_sm_count() * 8, 256, 0, s>>>((const unsigned char *)src, (unsigned char *)dst, nbytes);
+        bcopy_kernel<<<device_sm_count() * 8, 256, 0, s>>>((const unsigned char *)src, (unsigned char *)dst, nbytes); note_launch();
     }
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
@@ -359,7 +360,7 @@ extern "C" int32_t kf_setvalue(int32_t dtype, void *dst, uint64_t n, const void 
     const uintptr_t md = (uintptr_t)dst & 15u;
     u64 head = md ? 16 - md : 0;  // a multiple of the element size, so the pattern stays in phase
     if (head > nbytes) head = nbytes;
-    fill_kernel<256><<<stream_grid(nbytes, 256, 1), 256, 0, (cudaStream_t)stream>>>((unsigned char *)dst, nbytes, head, pattern);
+    fill_kernel<256><<<stream_grid(nbytes, 256, 1), 256, 0, (cudaStream_t)stream>>>((unsigned char *)dst, nbytes, head, pattern); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;
 }

@@ -7,8 +7,10 @@ Mirrors src/scan/scan.jl:218-284 of KernelForge.jl. Calling forms:
     scan_(AffineCompose(), (a_dst, b_dst), (a_src, b_src))      # two Float32 arrays
     scan_(AffineCompose(), dst_ab, src_ab)                      # [n, 2] Float32 (NTuple{2,Float32})
 
-`init=` (a one-element device tensor; (a, b) for the affine form) is folded in from the left; the
-sharded scan uses it to seed a shard with the carry of the shards before it.
+`g=` is applied to every output element (src/scan/scan_kernel.jl:463,470,474): identity or sqrt.
+`init=` (a device tensor of one or more elements; [k, 2] (a, b) pairs for the affine form) is folded
+left to right and seeds the scan from the left; the sharded scan passes the totals of the shards
+before it.
 """
 from __future__ import annotations
 
@@ -45,6 +47,7 @@ def _scan_affine(dst, src, init, tmp, cfg):
         with torch.cuda.device(src[0].device):
             rc = lib.kf_scan_affine_soa(src[0].data_ptr(), src[1].data_ptr(), dst[0].data_ptr(), dst[1].data_ptr(),
                                         n, init.data_ptr() if init is not None else None,
+                                        init.numel() // 2 if init is not None else 0,
                                         buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src[0]))
         C.check(rc, "scan!")
         return dst
@@ -59,24 +62,27 @@ def _scan_affine(dst, src, init, tmp, cfg):
     buf = resolve_tmp(tmp, Scan1D, scan_bytes(C.F32, True, n, cfg), src.device)
     with torch.cuda.device(src.device):
         rc = lib.kf_scan_affine_aos(src.data_ptr(), dst.data_ptr(), n, init.data_ptr() if init is not None else None,
+                                    init.numel() // 2 if init is not None else 0,
                                     buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src))
     C.check(rc, "scan!")
     return dst
 
 
-def scan_(*args, g=ops.identity, tmp=None, Nitem=None, workgroup=None, family=None, arch=None, init=None):
-    """`scan!([f,] op, dst, src)`: dst[i] = f(src[0]) op ... op f(src[i]). Returns dst (asynchronous)."""
+def scan_(*args, g=ops.identity, tmp=None, Nitem=None, workgroup=None, family=None, arch=None, init=None,
+          _test_hook=0):
+    """`scan!([f,] op, dst, src)`: dst[i] = g(f(src[0]) op ... op f(src[i])). Returns dst (asynchronous)."""
     f, op, dst, src = _split_args(args, 2)
-    if ops.post_code(g) != C.POST_IDENTITY:
-        raise C.ArgumentError("scan supports g=identity only in this library")
-    cfg = C.make_cfg(workgroup, Nitem, None)
+    gcode = ops.post_code(g)
+    cfg = C.make_cfg(workgroup, Nitem, None, _test_hook)
     if init is not None:
         ops.require_device_vector(init, "init")
+        if not init.is_contiguous():
+            raise C.ArgumentError("init must be contiguous")
     if isinstance(op, ops.AffineCompose):
-        if ops.map_code(f) != C.MAP_IDENTITY:
-            raise C.ArgumentError("AffineCompose supports f=identity only")
-        if init is not None and (init.dtype != torch.float32 or init.numel() != 2):
-            raise C.ArgumentError("init must be a Float32 (a, b) pair")
+        if ops.map_code(f) != C.MAP_IDENTITY or gcode != C.POST_IDENTITY:
+            raise C.ArgumentError("AffineCompose supports f=identity and g=identity only")
+        if init is not None and (init.dtype != torch.float32 or init.numel() == 0 or init.numel() % 2):
+            raise C.ArgumentError("init must hold Float32 (a, b) pairs")
         return _scan_affine(dst, src, init, tmp, cfg)
     fcode, opcode = ops.map_code(f), ops.op_code(op)
     ops.require_device_vector(src, "src")
@@ -86,15 +92,15 @@ def scan_(*args, g=ops.identity, tmp=None, Nitem=None, workgroup=None, family=No
     n = src.numel()
     if dst.numel() != n:
         raise C.ArgumentError("dst and src must have equal lengths")
-    if init is not None and (init.dtype != src.dtype or init.numel() != 1):
-        raise C.ArgumentError("init must be a one-element tensor of the element type")
+    if init is not None and (init.dtype != src.dtype or init.numel() < 1):
+        raise C.ArgumentError("init must hold one or more elements of the element type")
     if n == 0:
         return dst
     code = ops.dtype_code(src)
     buf = resolve_tmp(tmp, Scan1D, scan_bytes(code, False, n, cfg), src.device)
     with torch.cuda.device(src.device):
-        rc = C.load().kf_scan(fcode, opcode, code, src.data_ptr(), dst.data_ptr(), n,
-                              init.data_ptr() if init is not None else None,
+        rc = C.load().kf_scan(fcode, opcode, gcode, code, src.data_ptr(), dst.data_ptr(), n,
+                              init.data_ptr() if init is not None else None, init.numel() if init is not None else 0,
                               buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src))
     C.check(rc, "scan!")
     return dst

@@ -63,7 +63,7 @@ def main():
             cfg = ctypes.pointer(C.LaunchCfg(t, v, 0, 0))
 
             def f():
-                rc = lib.kf_scan(0, 0, C.F32, xf.data_ptr(), out.data_ptr(), n, None, ws.data_ptr(), ws.numel(), cfg, st)
+                rc = lib.kf_scan(0, 0, 0, C.F32, xf.data_ptr(), out.data_ptr(), n, None, 0, ws.data_ptr(), ws.numel(), cfg, st)
                 assert rc == 0, rc
             ms = timeit(f)
             kind = "persistent" if (t, v) in ((768, 4), (384, 8), (512, 8)) else "direct"

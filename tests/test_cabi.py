@@ -30,16 +30,16 @@ def test_header_symbols_are_exported_and_bound(kf):
 def test_header_cites_reference_for_every_entry(kf):
     text = open(HEADER).read()
     for name in declared_symbols():
-        m = re.search(r"^(?:int32_t|size_t|const char \*)\s*" + name + r"\(", text, flags=re.M)  # the declaration itself
+        m = re.search(r"^(?:int32_t|uint64_t|size_t|const char \*)\s*" + name + r"\(", text, flags=re.M)  # the declaration itself
         assert m, name
         i = m.start()
         comment = text[text.rfind("/*", 0, i):i]
-        assert re.search(r"\.jl:\d+|no counterpart|ABI version|last KF_ERR|SMs of the current", comment), name
+        assert re.search(r"\.jl:\d+|no\s+counterpart|ABI version|last KF_ERR|SMs of the current", comment, flags=re.I), name
 
 
 def test_version_and_error_strings(kf):
     lib = kf.lib
-    assert lib.kf_abi_version() == 1
+    assert lib.kf_abi_version() == 2
     texts = {lib.kf_error_string(i).decode() for i in range(7)}
     assert len(texts) == 7 and "ok" in texts
     assert "unknown" in lib.kf_error_string(99).decode()
@@ -89,10 +89,10 @@ def test_argument_errors_before_any_device_work(kf):
     assert lib.kf_mapreduce(0, 0, 1, C.I32, fake, 10, fake, fake, 1 << 20, None, None) == C.ERR_UNSUPPORTED  # sqrt of ints
     assert lib.kf_mapreduce(0, 0, 0, C.F32, fake, 1 << 20, fake, fake, 16, None, None) == C.ERR_WORKSPACE_TOO_SMALL
     assert lib.kf_mapreduce(0, 0, 0, C.F32, ctypes.c_void_p(0x1002), 10, fake, fake, 1 << 20, None, None) == C.ERR_INVALID_ARG
-    assert lib.kf_scan(0, 0, C.F32, fake, fake, 0, None, fake, 0, None, None) == C.OK  # n == 0 is a no-op
-    assert lib.kf_scan(0, C.OP_AFFINE, C.F32, fake, fake, 10, None, fake, 1 << 20, None, None) == C.ERR_UNSUPPORTED
-    assert lib.kf_scan(0, 0, C.F32, fake, fake, 1 << 20, None, fake, 8, None, None) == C.ERR_WORKSPACE_TOO_SMALL
-    assert lib.kf_scan(0, 0, 42, fake, fake, 10, None, fake, 1 << 20, None, None) == C.ERR_INVALID_ARG
+    assert lib.kf_scan(0, 0, 0, C.F32, fake, fake, 0, None, 0, fake, 0, None, None) == C.OK  # n == 0 is a no-op
+    assert lib.kf_scan(0, C.OP_AFFINE, 0, C.F32, fake, fake, 10, None, 0, fake, 1 << 20, None, None) == C.ERR_UNSUPPORTED
+    assert lib.kf_scan(0, 0, 0, C.F32, fake, fake, 1 << 20, None, 0, fake, 8, None, None) == C.ERR_WORKSPACE_TOO_SMALL
+    assert lib.kf_scan(0, 0, 0, 42, fake, fake, 10, None, 0, fake, 1 << 20, None, None) == C.ERR_INVALID_ARG
     assert lib.kf_sort_keys(C.U32, fake, fake, 0, fake, 0, None, None) == C.OK
     assert lib.kf_sort_keys(42, fake, fake, 10, fake, 1 << 20, None, None) == C.ERR_INVALID_ARG
     assert lib.kf_sort_pairs(C.U8, fake, fake, 2, fake, fake, 10, fake, 1 << 20, None, None) == C.ERR_UNSUPPORTED  # 2-byte payload

@@ -354,3 +354,64 @@ def test_random_sizes_offsets_variants(kf, oracle):
             h = pool[o2:o2 + 2 * (n // 2 + 1)].view(np.int64)
             got = to_host(kf.scan("max", dev32[o2:o2 + 2 * (n // 2 + 1)].view(torch.int64), **kw))
             assert (got == oracle.c_scan(0, 3, h)).all(), (it, n, off, var)
+
+
+@pytest.mark.parametrize("n", [7, 1000, 3_000_001])
+def test_post_map_g_on_every_output(kf, oracle, n):
+    """scan!(f, op, dst, src; g): g is applied to every output element, never to the carried prefix
+    (src/scan/scan_kernel.jl:463,470,474 of the reference): sqrt of the running sum of squares."""
+    x = np.random.default_rng(n).random(n).astype(np.float32)
+    got = to_host(kf.scan(kf.abs2, "+", to_dev(x), g=kf.sqrt))
+    ref = np.sqrt(oracle.c_scan(oracle.MAP_ABS2, oracle.OP_ADD, x))
+    assert_close_rel(got, ref, n)
+    xd = x.astype(np.float64)
+    gotd = to_host(kf.scan("+", to_dev(xd), g="sqrt", workgroup=256, Nitem=4))  # the direct kernel as well
+    assert_close_rel(gotd, np.sqrt(np.cumsum(xd)), n)
+    with pytest.raises(kf.ArgumentError):
+        kf.scan("+", to_dev(np.arange(10, dtype=np.int32)), g=kf.sqrt)  # sqrt of integers is not in the enum set
+
+
+@pytest.mark.parametrize("workgroup,nitem", [(256, 8), (384, 8)])
+def test_init_of_several_elements_is_folded_left_to_right(kf, oracle, workgroup, nitem):
+    """`init` with k elements seeds the scan with init[0] op ... op init[k-1] (what a shard of a sharded
+    scan passes: the totals of the shards before it)."""
+    rng = np.random.default_rng(5)
+    n = 2_000_003
+    x = rng.integers(0, 1 << 32, n, dtype=np.uint64).astype(np.uint32)
+    seeds = rng.integers(0, 1 << 32, 7, dtype=np.uint64).astype(np.uint32)
+    got = to_host(kf.scan("+", to_dev(x), init=to_dev(seeds), workgroup=workgroup, Nitem=nitem))
+    ref = oracle.c_scan(0, oracle.OP_ADD, np.concatenate([seeds, x]))[7:]
+    assert (got == ref).all()
+    # non-commutative: affine pairs, three seed pairs
+    a = (0.5 + 0.5 * rng.random(n)).astype(np.float32)
+    b = (2 * rng.random(n) - 1).astype(np.float32)
+    sa = (0.5 + 0.5 * rng.random(3)).astype(np.float32)
+    sb = (2 * rng.random(3) - 1).astype(np.float32)
+    init = to_dev(np.stack([sa, sb], axis=1).reshape(-1).copy())
+    da, db = kf.scan(kf.AffineCompose(), (to_dev(a), to_dev(b)), init=init, workgroup=workgroup, Nitem=nitem)
+    ra, rb = oracle.c_scan_affine(np.concatenate([sa, a]), np.concatenate([sb, b]))
+    tol = scan_tol(n)
+    assert (np.abs(to_host(db) - rb[3:]) <= tol * np.maximum(np.abs(rb[3:]), 1.0)).all()
+    assert (np.abs(to_host(da) - ra[3:]) <= tol * np.maximum(ra[3:], 4 * np.finfo(np.float32).tiny)).all()
+
+
+@pytest.mark.parametrize("workgroup,nitem,what", [(256, 8, "direct"), (384, 8, "persistent")])
+def test_bounded_wait_runs_out_and_the_workspace_recovers(kf, oracle, workgroup, nitem, what):
+    """A look-back whose predecessor never publishes gives up after its poll limit: the call returns,
+    kf_check reports KF_ERR_TIMEOUT with the tile that gave up, later tiles see the poison and return,
+    and the next call on the same workspace is correct. Nothing faults or hangs: the silent tile and
+    the short limit come through kf_launch_cfg.reserved (bits 16..31 = 1 + tile, bits 0..15 = polls)."""
+    from kernelforge_jl_b200 import _cabi as C
+    n = 40 * 384 * 8 * 4 + 17  # about 40 tiles of the persistent kernel, more of the direct one
+    x = np.random.default_rng(9).integers(0, 256, n).astype(np.uint32)
+    src = to_dev(x)
+    dst = torch.empty_like(src)
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", src, workgroup=workgroup, Nitem=nitem)
+    hook = ((1 + 3) << 16) | 400  # tile 3 stays silent; 400 polls (well under a millisecond each)
+    kf.scan_("+", dst, src, tmp=tmp, workgroup=workgroup, Nitem=nitem, _test_hook=hook)
+    assert kf.lib.kf_check(tmp.ptr(), None) == C.ERR_TIMEOUT
+    header = tmp.workspace[:8].view(torch.int32).cpu().numpy()
+    assert header[0] == C.ERR_TIMEOUT and header[1] >= 3  # word 1: the tile whose wait ran out
+    kf.scan_("+", dst, src, tmp=tmp, workgroup=workgroup, Nitem=nitem)  # same workspace, no hook
+    assert kf.lib.kf_check(tmp.ptr(), None) == C.OK
+    assert (to_host(dst) == oracle.c_scan(0, oracle.OP_ADD, x)).all()
