@@ -17,8 +17,10 @@ timed on this host; `primitives` lists the other configurations (mapreduce, affi
 measured the same way after the timed region.
 
 `--impl reference` times the reference's CPU path (Julia Base semantics restated in oracle/,
-the reference itself being Julia, which this machine does not have) with all host threads, on a
-bounded sample of the same workload.
+the reference itself being Julia, which this machine does not have) on the same step (n = 2^28 per
+array) with all host threads, the 1-thread figure beside it; both arms print the same `metric` and
+`config`. With N > 1 the GPU arm also reports the sharded mapreduce and the sample sort at 2^28 per
+GPU under `primitives`.
 """
 import argparse
 import json
@@ -35,6 +37,18 @@ if ROOT not in sys.path:
 
 N_HEADLINE = 1 << 28
 NOMINAL_HBM_GBS = 8000.0
+# One string for both arms: the driver divides the two lines only when metric, unit and direction agree.
+METRIC = "effective GB/s, inclusive scan(+), Float32 + UInt32 at n=2^28 per GPU"
+
+
+def workload_config(world):
+    """The `config` object of the JSON line, identical for the GPU arm and the reference arm."""
+    n = N_HEADLINE
+    return {"workload": "inclusive scan!(+, dst, x): Float32 x~U[0,1) n=2^28 and UInt32 x~U{0..255} n=2^28 "
+                        "per GPU" + ("" if world == 1 else "; sharded over %d GPUs (global n=%d*2^28): local "
+                                     "reduce, one NCCL allgather of the shard totals, seeded local scan" % (world, world)),
+            "n_per_gpu": n, "algorithmic_bytes_per_step": world * 2 * 8 * n,
+            "l2": "inputs (1 GiB per array) are larger than the 126 MB L2; no flush needed"}
 
 
 def measured_peak():
@@ -108,59 +122,112 @@ def host_threads():
         return max(1, os.cpu_count() or 1)
 
 
-def cpu_scan_sample(threads, n, repeats=3):
-    """Times accumulate(+) over Float32 and UInt32 arrays of n elements; returns (GB/s, seconds per pass)."""
-    import numpy as np
-    from oracle import oracle as O
-    rng = np.random.default_rng(0)
-    xf = rng.random(n, dtype=np.float32)
-    xu = rng.integers(0, 256, n).astype(np.uint32)
-    of, ou = np.empty_like(xf), np.empty_like(xu)
-    O.base_accumulate(xf, of, threads)  # warm the pages
-    O.base_accumulate(xu, ou, threads)
-    best = float("inf")
-    for _ in range(repeats):
+class CpuScanWorkload:
+    """Host arrays of the headline step (Float32 U[0,1) and UInt32 U{0..255}, n elements each) and the
+    Base-like accumulate over both, timed with the wall clock."""
+
+    def __init__(self, n, seed=0):
+        import numpy as np
+        from oracle import oracle as O
+        self.O, self.n = O, n
+        rng = np.random.default_rng(seed)
+        self.xf = rng.random(n, dtype=np.float32)
+        self.xu = np.frombuffer(rng.bytes(n), dtype=np.uint8).astype(np.uint32)  # uniform over {0..255}
+        self.of, self.ou = np.empty_like(self.xf), np.empty_like(self.xu)
+        self.nbytes = 2 * 8 * n
+
+    def step(self, threads):
         t0 = time.perf_counter()
-        O.base_accumulate(xf, of, threads)
-        O.base_accumulate(xu, ou, threads)
-        best = min(best, time.perf_counter() - t0)
-    return 2 * 8 * n / best / 1e9, best
+        self.O.base_accumulate(self.xf, self.of, threads)
+        self.O.base_accumulate(self.xu, self.ou, threads)
+        return time.perf_counter() - t0
+
+    def best_gbs(self, threads, repeats):
+        self.step(threads)  # warm the pages
+        return self.nbytes / min(self.step(threads) for _ in range(repeats)) / 1e9
 
 
-def cpu_baseline_object(threads, n):
-    gbs, secs = cpu_scan_sample(threads, n)
-    gbs1, _ = cpu_scan_sample(1, n, repeats=2) if threads > 1 else (gbs, secs)
+def cpu_baseline_object(work, threads):
+    gbs = work.best_gbs(threads, 3)
+    gbs1 = work.best_gbs(1, 2) if threads > 1 else gbs
     return {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
             "value_1_thread": round(gbs1, 3),
-            "sample": "accumulate(+) over Float32 and UInt32 arrays of n=2^%d (1/%d of the 2^28 workload), "
-                      "best of 3, C restatement of Base.accumulate (oracle/kf_oracle.c)" % (
-                          n.bit_length() - 1, N_HEADLINE // n)}
+            "sample": "one full step: accumulate(+) over the Float32 and the UInt32 array of n=2^%d each, best of 3 "
+                      "(1 thread: best of 2), C restatement of Base.accumulate (oracle/kf_oracle.c); the 1-thread figure "
+                      "is the faithful stand-in for Julia's single-threaded Base.accumulate" % (work.n.bit_length() - 1)}
+
+
+def cpu_primitive_legs(work, threads):
+    """CPU figures for the other primitives (Base-like C code of oracle/, 1 thread and all cores)."""
+    import numpy as np
+    O = work.O
+    out = {}
+
+    def both(fn, nbytes):
+        res = {}
+        for name, t in (("cpu_1_thread", 1), ("cpu_all_cores", threads)):
+            best = float("inf")
+            for _ in range(2):
+                t0 = time.perf_counter()
+                fn(t)
+                best = min(best, time.perf_counter() - t0)
+            res[name] = {"GB/s": round(nbytes / best / 1e9, 2), "ms": round(best * 1e3, 2)}
+        res["cores"] = threads
+        return res
+
+    n = work.n
+    out["mapreduce_f32_sum_2p28"] = both(lambda t: O.base_mapreduce_add_f32(O.MAP_IDENTITY, work.xf, t), 4 * n)
+    ns = 1 << 26
+    rng = np.random.default_rng(1)
+    keys = rng.integers(0, 1 << 32, ns, dtype=np.uint64).astype(np.uint32)
+    kk, tk = np.empty_like(keys), np.empty_like(keys)
+    vals, tv = np.empty(ns, dtype=np.uint32), np.empty(ns, dtype=np.uint32)
+
+    def sort_keys(t):
+        np.copyto(kk, keys)
+        O.base_sort_k32(kk, None, tk, None, t)
+
+    def sort_pairs(t):
+        np.copyto(kk, keys)
+        vals[:] = np.arange(ns, dtype=np.uint32)
+        O.base_sort_k32(kk, vals, tk, tv, t)
+
+    r = both(sort_keys, 36 * ns)
+    r["sample"] = "n=2^26 keys (1/4 of the GPU case; the timed call includes the copy that restores the unsorted keys)"
+    out["sort_u32_keys_2p28"] = r
+    r = both(sort_pairs, 68 * ns)
+    r["sample"] = "n=2^26 pairs (1/4 of the GPU case; includes restoring keys and payload)"
+    out["sort_u32_keys_u32_payload_2p28"] = r
+    return out
 
 
 def run_reference_arm(args):
+    """The reference's CPU path for the headline step (Base.accumulate restated in oracle/kf_oracle.c:
+    KernelForge.jl itself is Julia, which this machine does not have), on the full n = 2^28 per array,
+    with all host threads as `value` and the 1-thread figure beside it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    from oracle import oracle as O
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     threads = host_threads()
-    n = 1 << 26
+    work = CpuScanWorkload(N_HEADLINE)
     for _ in range(args.warmup):
-        cpu_scan_sample(threads, n, repeats=1)
+        work.step(threads)
     t0 = time.perf_counter()
-    vals = [cpu_scan_sample(threads, n, repeats=1) for _ in range(args.steps)]
+    secs = sum(work.step(threads) for _ in range(args.steps))
     wall = time.perf_counter() - t0
-    secs = sum(v[1] for v in vals)
-    gbs = args.steps * 2 * 8 * n / secs / 1e9
+    gbs = args.steps * work.nbytes / secs / 1e9
+    gbs1 = work.best_gbs(1, 2) if threads > 1 else gbs
+    sample = ("each step = the Float32 and the UInt32 array of n=2^28 (one GPU's share of the workload: 2 GiB in, "
+              "2 GiB out), all %d host threads; KernelForge.jl is Julia (not installed here), so the CPU path is the C "
+              "restatement of Base.accumulate in oracle/kf_oracle.c" % threads)
     line = {
-        "impl": "reference", "metric": "effective GB/s, inclusive scan(+), Float32 + UInt32", "value": round(gbs, 3),
-        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(1e3 * secs / args.steps, 3), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32+u32", "data": "synthetic",
-        "config": {"workload": "inclusive scan!(+): Float32 U[0,1) and UInt32 U{0..255}; CPU sample n=2^26 per array "
-                               "per step (1/4 of the 2^28 GPU workload)", "threads": threads},
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * secs / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+u32", "data": "synthetic",
+        "config": workload_config(world),
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": "n=2^26 per array per step; KernelForge.jl is Julia (not installed here), so the "
-                                   "CPU path is the C restatement of Base.accumulate in oracle/kf_oracle.c"},
+                         "value_1_thread": round(gbs1, 3), "sample": sample},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": round(wall, 2),
     }
@@ -202,10 +269,19 @@ def primitives_table(kf, torch, peak, iters=10):
     for _ in range(3):
         fn()
     add("mapreduce_f32_sum_2p28", 4 * n, time_gpu(fn, iters * 2, torch), 1)
-    fn = lambda: kf.mapreduce_(kf.abs2, "+", dst1, xf[: 1 << 20], tmp=tmp)
-    for _ in range(3):
+    # BASELINE config 1 (n = 2^20, launch-bound): the bare C-ABI call, as a Julia `ccall` would issue it
+    from kernelforge_jl_b200 import _cabi as C
+    small, st = xf[: 1 << 20], torch.cuda.current_stream().cuda_stream
+    args1 = (C.MAP_ABS2, C.OP_ADD, C.POST_IDENTITY, C.F32, small.data_ptr(), 1 << 20, dst1.data_ptr(), tmp.ptr(), tmp.nbytes, None, st)
+
+    def fn():
+        if kf.lib.kf_mapreduce(*args1) != 0:
+            raise SystemExit("bench: kf_mapreduce failed")
+    for _ in range(20):
         fn()
-    add("mapreduce_f32_abs2_2p20", 4 << 20, time_gpu(fn, 200, torch), 1)
+    add("mapreduce_f32_abs2_2p20", 4 << 20, time_gpu(fn, 1000, torch), 1)
+    out["mapreduce_f32_abs2_2p20"]["note"] = ("per call of kf_mapreduce through ctypes, 1000 back-to-back calls: one "
+                                              "256-byte memset + one kernel; launch-bound")
     yf = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
     fn = lambda: kf.mapreduce_(kf.prod, "+", dst1, (xf, yf), tmp=tmp)
     for _ in range(3):
@@ -271,9 +347,13 @@ def run_case(args):
     n = 1 << args.log2n
     g = torch.Generator(device="cuda").manual_seed(0)
     case = args.case
-    if case in ("scan_u32", "scan_f32", "mapreduce_f32"):
-        x = (torch.randint(0, 256, (n,), dtype=torch.int32, device="cuda", generator=g).view(torch.uint32)
-             if case == "scan_u32" else torch.rand(n, dtype=torch.float32, device="cuda", generator=g))
+    if case in ("scan_u32", "scan_f32", "scan_f64", "scan_u8", "mapreduce_f32"):
+        if case == "scan_u32":
+            x = torch.randint(0, 256, (n,), dtype=torch.int32, device="cuda", generator=g).view(torch.uint32)
+        elif case == "scan_u8":
+            x = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=g)
+        else:
+            x = torch.rand(n, dtype=torch.float64 if case == "scan_f64" else torch.float32, device="cuda", generator=g)
         if case == "mapreduce_f32":
             dst = torch.empty(1, dtype=torch.float32, device="cuda")
             tmp = kf.get_allocation(kf.MapReduce1D, kf.identity, "+", x)
@@ -281,7 +361,7 @@ def run_case(args):
         else:
             dst = torch.empty_like(x)
             tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", x)
-            fn, nbytes = (lambda: kf.scan_("+", dst, x, tmp=tmp)), 8 * n
+            fn, nbytes = (lambda: kf.scan_("+", dst, x, tmp=tmp)), 2 * x.element_size() * n
     elif case == "scan_affine":
         a = 0.5 + 0.5 * torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
         b = 2.0 * torch.rand(n, dtype=torch.float32, device="cuda", generator=g) - 1.0
@@ -424,6 +504,89 @@ def run_sharded(args):
     return 0
 
 
+def pin_rank_to_core_slice(local, world):
+    """Gives each rank its own slice of the visible cores (before any pinned allocation, so that the
+    pinned pages and the copy threads of a rank stay on one socket's cores)."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        if world > 1 and len(cores) >= world:
+            per = len(cores) // world
+            os.sched_setaffinity(0, cores[local * per:(local + 1) * per])
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return None
+
+
+def sharded_primitives(kf, kfd, torch, dist, group, peak, iters):
+    """The other two primitives on the sharded layout, 2^28 elements per GPU (weak scaling): mapreduce(+)
+    over Float32 (local kernel + NCCL allreduce) and the sample sort of uniform UInt32 keys (partition
+    pass, NCCL all-to-all, local onesweep). Device-timed, max over ranks, checked by size-independent
+    properties. Returns {name: {...}} on every rank."""
+    world, rank = group.world, group.rank
+    n = N_HEADLINE
+    g = torch.Generator(device="cuda").manual_seed(5000 + rank)
+
+    def timed(fn, k):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(k):
+            fn()
+        b.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / k], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {}
+
+    def add(name, nbytes, ms, note):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_of_measured_peak_x_gpus": round(gbs / (peak * world), 4),
+                     "frac_of_nominal_8TBs_x_gpus": round(gbs / (NOMINAL_HBM_GBS * world), 4),
+                     "algorithmic_bytes": nbytes, "note": note}
+
+    xf = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+    ms = timed(lambda: kfd.mapreduce(group, kf.identity, "+", xf, to_cpu=False), iters)
+    got = kfd.mapreduce(group, kf.identity, "+", xf)
+    ref = xf.sum(dtype=torch.float64)
+    dist.all_reduce(ref)
+    if abs(got - ref.item()) > 1e-5 * 32 * ref.item():
+        raise SystemExit("bench: sharded mapreduce is off: %r vs %r" % (got, ref.item()))
+    add("sharded_mapreduce_f32_sum_2p28_per_gpu", 4 * n * world, ms, "local mapreduce + NCCL allreduce of one partial per rank")
+    del xf
+
+    keys = torch.randint(0, 1 << 32, (n,), dtype=torch.int64, device="cuda", generator=g).to(torch.int32).view(torch.uint32)
+    k64 = keys.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    chk = torch.stack([k64.sum(), (k64 * k64 + 7 * k64).sum()])
+    del k64
+    dist.all_reduce(chk)
+    holder = {}
+
+    def do_sort():
+        holder["r"] = kfd.sort(group, keys)
+    ms = timed(do_sort, max(2, iters // 4))
+    chunk, counts = holder["r"]
+    c64 = chunk.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    ok = sum(counts) == n * world and bool((c64[1:] >= c64[:-1]).all().item())
+    chk2 = torch.stack([c64.sum(), (c64 * c64 + 7 * c64).sum()])
+    dist.all_reduce(chk2)
+    edge = torch.stack([c64[0], c64[-1]])
+    edges = [torch.zeros_like(edge) for _ in range(world)]
+    dist.all_gather(edges, edge)
+    ok = ok and torch.equal(chk, chk2) and all(int(edges[r][0]) >= int(edges[r - 1][1]) for r in range(1, world))
+    if not ok:
+        raise SystemExit("bench: sample sort failed its checks (sortedness, checksums, piece boundaries)")
+    add("sample_sort_u32_keys_2p28_per_gpu", 36 * n * world, ms,
+        "4096 stratified samples per GPU, one partition pass, NCCL all-to-all, local onesweep; largest piece / mean = %.4f"
+        % (max(counts) / n))
+    return out
+
+
 def run_gpu_arm(args):
     import numpy as np
     import torch
@@ -435,6 +598,7 @@ def run_gpu_arm(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    cores_of_rank = pin_rank_to_core_slice(local, world)
     torch.cuda.set_device(local)
     kf = load_package()
     from kernelforge_jl_b200 import distributed as kfd
@@ -442,6 +606,7 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peak, peak_kind = measured_peak()
     n = N_HEADLINE
+    warm = max(args.warmup, 3)
 
     # Each rank owns shard `rank` of a global array of world*n elements (seeded per shard).
     g = torch.Generator(device="cuda").manual_seed(1000 + rank)
@@ -456,18 +621,15 @@ def run_gpu_arm(args):
         if world == 1:
             kf.scan_("+", df, xf, tmp=tmp_f)
             kf.scan_("+", du, xu, tmp=tmp_u)
-        else:
-            kfd.scan_(group, "+", df, xf, tmp=tmp_f)
-            kfd.scan_(group, "+", du, xu, tmp=tmp_u)
-
-    launches_per_step = 2 if world == 1 else 6  # sharded: reduce + scan of the shard totals + seeded scan, per array
+        else:  # both arrays with one exchange: 2 reductions, one allgather, 2 seeded scans
+            kfd.scan_many_(group, [("+", df, xf, tmp_f), ("+", du, xu, tmp_u)])
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warm):
         step()
     barrier()
     # The timed region (K steps of < 1 ms) is shorter than one nvidia-smi sampling period, so the
@@ -491,11 +653,13 @@ def run_gpu_arm(args):
         step()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    launches0 = int(kf.lib.kf_launch_count())
     start.record()
     for _ in range(args.steps):
         step()
     stop.record()
     barrier()
+    launches = int(kf.lib.kf_launch_count()) - launches0  # kernels of libkf_b200.so launched by this rank in the timed region
     ms = start.elapsed_time(stop)
     for _ in range(tail):
         step()
@@ -511,37 +675,55 @@ def run_gpu_arm(args):
     step_bytes = world * 2 * 8 * n
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # quick device-side sanity of the timed outputs (wrapping differences reproduce the input)
-    ok = bool(((du.view(torch.int32)[1:] - du.view(torch.int32)[:-1]) == xu.view(torch.int32)[1:]).all().item())
+    # Device-side sanity of the timed outputs: wrapping first differences reproduce the input inside the
+    # shard, and the shard's first output equals the carry of the shards before it plus its first input
+    # (so a wrong carry across a shard boundary cannot pass).
+    d32, x32 = du.view(torch.int32), xu.view(torch.int32)
+    ok = bool(((d32[1:] - d32[:-1]) == x32[1:]).all().item())
+    if world > 1:
+        tot = x32.sum(dtype=torch.int64).reshape(1)
+        tots = [torch.zeros_like(tot) for _ in range(world)]
+        dist.all_gather(tots, tot)
+        carry = sum(int(t.item()) for t in tots[:rank])
+        ok = ok and ((int(d32[0].item()) - int(x32[0].item()) - carry) & 0xFFFFFFFF) == 0
+        fl = xf.sum(dtype=torch.float64).reshape(1)
+        fls = [torch.zeros_like(fl) for _ in range(world)]
+        dist.all_gather(fls, fl)
+        want = sum(float(t.item()) for t in fls[: rank + 1])
+        ok = ok and abs(float(df[-1].item()) - want) <= 1e-5 * 32 * want
     if not ok:
-        raise SystemExit("bench: scan output failed its difference check")
+        raise SystemExit("bench: scan output failed its difference / shard-boundary check")
 
     # ---- roofline of the dominant kernel: the UInt32/Float32 look-back scan kernel, single GPU view
     kern_ms = time_gpu(lambda: kf.scan_("+", du, xu, tmp=tmp_u), 20, torch)
     achieved = 8 * n / (kern_ms * 1e-3) / 1e9
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    traffic = traffic_how = None
     try:
-        with open(tpath) as fh:
-            traffic = json.load(fh).get("scan_kernel_roles_u32_2p28_bytes_per_launch")
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as fh:
+            tj = json.load(fh)
+        # DRAM reads grow with n (measured ratio to the input at n = 2^26); the output is written once.
+        # (Scaling the small case's WRITE counter would undercount: about 58 MB of the output are still
+        # in L2 when the kernel ends, a constant, not a share of n.)
+        traffic = int(round(tj["scan_kernel_roles_u32_read_ratio"] * 4 * n + 4 * n))
+        traffic_how = tj["_how"]
     except Exception:
         pass
     # The same kernel and a plain copy under SUSTAINED load (0.5 s of back-to-back launches first: the
     # 1 kW power cap then lowers the SM clock), and the headline steps timed as a burst after an idle
     # pause: the two regimes MEASURED_PEAKS.json distinguishes.
-    sustained = burst = None
+    def sustained_ms(fn, iters):
+        t_end = time.perf_counter() + 0.5
+        while time.perf_counter() < t_end:
+            for _ in range(50):
+                fn()
+            torch.cuda.synchronize()
+        return time_gpu(fn, iters, torch)
+    k_ms = sustained_ms(lambda: kf.scan_("+", du, xu, tmp=tmp_u), 20)
+    c_ms = sustained_ms(lambda: du.copy_(xu), 20)
+    sustained = {"achieved": round(8 * n / (k_ms * 1e-3) / 1e9, 1), "copy_measured_here": round(8 * n / (c_ms * 1e-3) / 1e9, 1),
+                 "frac_of_copy": round(c_ms / k_ms, 4), "unit": "GB/s"}
+    burst = None
     if world == 1:
-        def sustained_ms(fn, iters):
-            t_end = time.perf_counter() + 0.5
-            while time.perf_counter() < t_end:
-                for _ in range(50):
-                    fn()
-                torch.cuda.synchronize()
-            return time_gpu(fn, iters, torch)
-        k_ms = sustained_ms(lambda: kf.scan_("+", du, xu, tmp=tmp_u), 20)
-        c_ms = sustained_ms(lambda: du.copy_(xu), 20)
-        sustained = {"achieved": round(8 * n / (k_ms * 1e-3) / 1e9, 1), "copy_measured_here": round(8 * n / (c_ms * 1e-3) / 1e9, 1),
-                     "frac_of_copy": round(c_ms / k_ms, 4), "unit": "GB/s"}
         torch.cuda.synchronize()
         time.sleep(0.5)
         b_ms = time_gpu(step, args.steps, torch)
@@ -551,67 +733,98 @@ def run_gpu_arm(args):
                 "peak": peak, "peak_kind": peak_kind + " (STREAM-style copy)", "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                 "algorithmic_bytes_per_launch": 8 * n, "kernel_ms": round(kern_ms, 4), "traffic": traffic,
-                "sustained": sustained}
+                "traffic_how": traffic_how, "sustained": sustained}
 
     # ---- end to end through the host-buffer API: pinned host arrays in, host arrays out
-    e2e = None
-    if True:
-        hf = torch.empty(n, dtype=torch.float32).pin_memory()
-        hu = torch.empty(n, dtype=torch.int32).pin_memory()
-        hf.copy_(xf)
-        hu.copy_(xu.view(torch.int32))
-        of = torch.empty(n, dtype=torch.float32).pin_memory()
-        ou = torch.empty(n, dtype=torch.int32).pin_memory()
-        pipe = kfd.HostScanPipeline(kf, n, chunk_bytes=args.e2e_chunk_mb << 20, slots=4)
+    hf = torch.empty(n, dtype=torch.float32).pin_memory()
+    hu = torch.empty(n, dtype=torch.int32).pin_memory()
+    hf.copy_(xf)
+    hu.copy_(xu.view(torch.int32))
+    of = torch.empty(n, dtype=torch.float32).pin_memory()
+    ou = torch.empty(n, dtype=torch.int32).pin_memory()
+    pipe = kfd.HostScanPipeline(kf, n, chunk_bytes=args.e2e_chunk_mb << 20, slots=4)
 
-        def e2e_step():
-            pipe.scan_host_many([("+", of, hf),
-                                 ("+", ou.view(torch.uint32) if hasattr(torch, "uint32") else ou, hu.view(torch.uint32))])
+    def e2e_step():
+        pipe.scan_host_many([("+", of, hf), ("+", ou.view(torch.uint32), hu.view(torch.uint32))])
 
+    def timed_host(fn, k):
         for _ in range(2):
-            e2e_step()
+            fn()
         barrier()
-        t0 = time.perf_counter()
-        e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e_start.record()
-        e_steps = max(2, min(args.steps, 5))
-        for _ in range(e_steps):
-            e2e_step()
-        e_stop.record()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(k):
+            fn()
+        b.record()
         barrier()
-        e_ms = e_start.elapsed_time(e_stop) / e_steps
+        v = a.elapsed_time(b) / k
         if world > 1:
-            t = torch.tensor([e_ms], dtype=torch.float64, device="cuda")
+            t = torch.tensor([v], dtype=torch.float64, device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms = float(t.item())
-        okh = bool((ou[1:] - ou[:-1] == hu[1:]).all().item())
-        if not okh:
-            raise SystemExit("bench: host-pipeline scan output failed its difference check")
-        e2e = {"value": round(world * 2 * 8 * n / (e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
-               "h2d_bytes_per_step": 2 * 4 * n, "d2h_bytes_per_step": 2 * 4 * n, "ms_per_step": round(e_ms, 3),
-               "note": "independent per-rank host arrays; %d MiB chunks through a 4-slot device ring: H2D / scan(init=carry) / D2H on three streams" % args.e2e_chunk_mb}
-        del hf, hu, of, ou, pipe
+            v = float(t.item())
+        return v
 
-    line = None
+    e_steps = max(2, min(args.steps, 5))
+    e_ms = timed_host(e2e_step, e_steps)
+    if not bool((ou[1:] - ou[:-1] == hu[1:]).all().item()):
+        raise SystemExit("bench: host-pipeline scan output failed its difference check")
+
+    # The ceiling of that number: the same bytes as plain pinned copies in both directions at once (no
+    # kernel), on all ranks at the same time.
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def copy_only():
+        cur = torch.cuda.current_stream()
+        s_up.wait_stream(cur)
+        s_down.wait_stream(cur)
+        with torch.cuda.stream(s_up):
+            df.copy_(hf, non_blocking=True)
+            du.view(torch.int32).copy_(hu, non_blocking=True)
+        with torch.cuda.stream(s_down):
+            of.copy_(xf, non_blocking=True)
+            ou.copy_(xu.view(torch.int32), non_blocking=True)
+        cur.wait_stream(s_up)
+        cur.wait_stream(s_down)
+    c_host_ms = timed_host(copy_only, e_steps)
+    e2e = {"value": round(world * 2 * 8 * n / (e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+           "h2d_bytes_per_step": 2 * 4 * n, "d2h_bytes_per_step": 2 * 4 * n, "ms_per_step": round(e_ms, 3),
+           "copy_ceiling": {"value": round(world * 2 * 8 * n / (c_host_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                            "ms_per_step": round(c_host_ms, 3),
+                            "what": "the same 2 GiB up and 2 GiB down per rank as plain pinned-memory copies on two "
+                                    "streams, all %d ranks at once, no kernel: what the host side of the box delivers" % world},
+           "frac_of_copy_ceiling": round(c_host_ms / e_ms, 4), "host_cores_of_this_rank": cores_of_rank,
+           "note": "independent per-rank host arrays; %d MiB chunks through a 4-slot device ring: H2D / scan(init=carry) / D2H on three streams" % args.e2e_chunk_mb}
+    del hf, hu, of, ou, pipe
+
+    prim = None
+    if args.detail:
+        if world == 1:
+            prim = primitives_table(kf, torch, peak)
+        else:
+            prim = sharded_primitives(kf, kfd, torch, dist, group, peak, max(4, args.steps // 2))
+
     if rank == 0:
-        from oracle import oracle as O
-        cpu = cpu_baseline_object(host_threads(), 1 << 26)
-        prim = primitives_table(kf, torch, peak) if (args.detail and world == 1) else None
         line = {
-            "metric": "effective GB/s, inclusive scan(+), Float32 + UInt32 at n=2^28 per GPU", "value": round(value, 1),
-            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": METRIC, "value": round(value, 1),
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "warmup_run": warm,
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32+u32", "data": "synthetic",
             "frac_of_measured_peak": round(value / (peak * world), 4),
             "frac_of_nominal_8TBs": round(value / (NOMINAL_HBM_GBS * world), 4),
-            "config": {"workload": "inclusive scan!(+, dst, x): Float32 x~U[0,1) n=2^28 and UInt32 x~U{0..255} n=2^28 "
-                                   "per GPU" + ("" if world == 1 else "; sharded over %d GPUs (global n=%d*2^28): local "
-                                                "reduce, NCCL allgather of shard totals, seeded local scan" % (world, world)),
-                       "n_per_gpu": n, "algorithmic_bytes_per_step": step_bytes,
-                       "l2": "inputs (1 GiB per array) are larger than the 126 MB L2; no flush needed"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+            "config": workload_config(world),
+            "roofline": roofline, "e2e": e2e, "gpu_launches": launches,
+            "gpu_launches_how": "kf_launch_count() of libkf_b200.so before and after the timed region on rank 0 (%s per step)"
+                                % ("2 scan kernels" if world == 1 else "2 reductions + 2 seeded scans; the allgather is NCCL's"),
             "clocks": clocks, "burst": burst,
         }
+        if world == 1:
+            work = CpuScanWorkload(n)
+            threads = host_threads()
+            line["cpu_baseline"] = cpu_baseline_object(work, threads)
+            if prim is not None:
+                for k, v in cpu_primitive_legs(work, threads).items():
+                    if k in prim:
+                        prim[k]["cpu"] = v
         if prim is not None:
             line["primitives"] = prim
         print(json.dumps(line))
@@ -630,7 +843,7 @@ def main():
     ap.add_argument("--detail", type=int, default=1, help="1: also measure the other primitives (single GPU)")
     ap.add_argument("--case", default=None,
                     help="run ONE primitive a few times at n=2^log2n and exit (small case for profiler captures): "
-                         "scan_u32, scan_f32, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_pairs")
+                         "scan_u32, scan_f32, scan_f64, scan_u8, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_pairs")
     ap.add_argument("--log2n", type=int, default=26)
     ap.add_argument("--sharded", action="store_true",
                     help="measure the sharded configuration instead (mapreduce, scan and sample sort over one global "

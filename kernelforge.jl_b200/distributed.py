@@ -5,11 +5,12 @@ rank owns one contiguous shard of a global array (rank order = array order) and 
 "local kernel(s) + ONE small exchange":
 
   mapreduce : local mapreduce -> allreduce of one partial per rank (allgather + ordered fold for
-              the operators NCCL cannot reduce) -> g.
-  scan      : local reduce -> allgather of the shard totals -> exclusive fold of the totals in
-              rank order -> local scan seeded with the carry (12n bytes instead of the 16n of
-              "scan, then fix up"). Non-commutative operators (AffineCompose) take the ordered
-              route: local scan for the total, then the seeded scan.
+              the operators NCCL cannot reduce) -> g (on the host when the value goes there anyway).
+  scan      : local reduce -> allgather of the shard totals -> local scan seeded with the totals of
+              the shards before it, which the scan kernel folds itself in rank order (12n bytes
+              instead of the 16n of "scan, then fix up", and no kernel for the carry). `scan_many_`
+              does this for several arrays with ONE allgather. Non-commutative operators
+              (AffineCompose) take the ordered route: local scan for the total, then the seeded scan.
   sort      : samples of the shard, allgather, identical splitter choice everywhere -> cut the shard
               into one run per destination -> all-to-all of the runs (NCCL, over NVLink) -> local
               onesweep sort of what arrived (keys only, so stable order is irrelevant and the result
@@ -44,13 +45,23 @@ class ShardGroup:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self._scratch = {}
+
+    def scratch(self, name, numel, dtype, device):
+        """A small reusable tensor (partials, gathered totals): allocated once per (name, shape, type)."""
+        key = (name, numel, dtype, device)
+        t = self._scratch.get(key)
+        if t is None:
+            t = self._scratch[key] = torch.empty(numel, dtype=dtype, device=device)
+        return t
 
 
 class LocalOps:
     """Local (per-shard) steps on the GPU through libkf_b200.so."""
 
-    def reduce(self, f, op, x):
-        out = torch.empty(1, dtype=x.dtype, device=x.device)
+    def reduce(self, f, op, x, out=None):
+        if out is None:
+            out = torch.empty(1, dtype=x.dtype, device=x.device)
         return mapreduce_(f, op, out, x)
 
     def fold(self, op, partials, g=ops.identity):
@@ -128,25 +139,38 @@ def mapreduce(group: ShardGroup, f, op, x, *, g=ops.identity, local: LocalOps = 
     opcode = ops.op_code(op)
     if opcode == C.OP_AFFINE:
         raise C.ArgumentError("AffineCompose is not commutative: use scan")
-    part = local.reduce(f, op, x)
+    gcode = ops.post_code(g)
+    part = local.reduce(f, op, x, out=group.scratch("partial", 1, x.dtype, x.device))
     if opcode in _NCCL_REDUCE and part.dtype in _NCCL_DTYPES:
         dist.all_reduce(part, op=_NCCL_REDUCE[opcode], group=group.group)
-        total = local.fold(op, part, g=g)  # one element: applies g
+        if gcode == C.POST_IDENTITY:
+            total = part
+        elif to_cpu:  # g on the host side of the read-back: no second kernel for one element
+            v = part.cpu()[0].item()
+            if gcode == C.POST_SQRT:
+                return v ** 0.5
+            raise C.ArgumentError("unknown post-map")
+        else:
+            total = local.fold(op, part, g=g)
     else:
         total = local.fold(op, all_gather_vec(group, part), g=g)
     return total.cpu()[0].item() if to_cpu else total
 
 
 # ---- scan ----------------------------------------------------------------------------------------
-def scan_(group: ShardGroup, *args, tmp=None, local: LocalOps = _DEFAULT_OPS):
-    """Sharded `scan!([f,] op, dst, src)`: dst holds this rank's shard of the global inclusive scan."""
+def _unpack_scan_args(args):
     if len(args) == 3:
-        f, (op, dst, src) = ops.identity, args
-    else:
-        f, op, dst, src = args
+        return (ops.identity,) + tuple(args)
+    return tuple(args)
+
+
+def scan_(group: ShardGroup, *args, tmp=None, g=ops.identity, local: LocalOps = _DEFAULT_OPS):
+    """Sharded `scan!([f,] op, dst, src)`: dst holds this rank's shard of the global inclusive scan."""
+    f, op, dst, src = _unpack_scan_args(args)
     affine = isinstance(op, ops.AffineCompose)
+    kw = {} if ops.post_code(g) == C.POST_IDENTITY else {"g": g}
     if group.world == 1:
-        return local.scan_(f, op, dst, src, tmp=tmp)  # a single shard needs no carry
+        return local.scan_(f, op, dst, src, tmp=tmp, **kw)  # a single shard needs no carry
     if affine:
         # ordered route: the shard total is the last element of a local scan
         local.scan_(f, op, dst, src, tmp=tmp)
@@ -154,18 +178,41 @@ def scan_(group: ShardGroup, *args, tmp=None, local: LocalOps = _DEFAULT_OPS):
             total = torch.stack([dst[0][-1], dst[1][-1]])
         else:
             total = dst[-1].clone()
-        totals = all_gather_vec(group, total).view(group.world, 2)
+        totals = all_gather_vec(group, total)  # (a, b) pairs in rank order
         if group.rank == 0:
             return dst
-        carry = local.scan_(f, op, torch.empty_like(totals), totals)[group.rank - 1].contiguous()
-        return local.scan_(f, op, dst, src, init=carry, tmp=tmp)
-    total = local.reduce(f, op, src)
+        return local.scan_(f, op, dst, src, init=totals[: 2 * group.rank], tmp=tmp)
+    total = local.reduce(f, op, src, out=group.scratch("partial", 1, src.dtype, src.device))
     totals = all_gather_vec(group, total)
-    init = None
+    # the scan kernel folds the totals of the shards before this one itself (ninit = rank)
+    init = totals[: group.rank] if group.rank > 0 else None
+    return local.scan_(f, op, dst, src, init=init, tmp=tmp, **kw)
+
+
+def scan_many_(group: ShardGroup, jobs, *, local: LocalOps = _DEFAULT_OPS):
+    """Several sharded scans with ONE exchange: `jobs` are (op, dst, src) or (op, dst, src, tmp) tuples of
+    commutative-or-not elementwise operators on arrays whose elements have the same size (AffineCompose
+    goes through `scan_`). All local reductions first, one allgather of every job's shard total, then
+    the seeded scans."""
+    if group.world == 1:
+        return [local.scan_(ops.identity, j[0], j[1], j[2], tmp=j[3] if len(j) > 3 else None) for j in jobs]
+    first = jobs[0][2]
+    es, dev, k = first.element_size(), first.device, len(jobs)
+    if any(isinstance(j[0], ops.AffineCompose) or j[2].element_size() != es for j in jobs):
+        raise C.ArgumentError("scan_many_ takes elementwise operators on arrays of one element size")
+    mine = group.scratch("many_partials", k * es, torch.uint8, dev)
+    for i, j in enumerate(jobs):
+        local.reduce(ops.identity, j[0], j[2], out=mine[i * es:(i + 1) * es].view(j[2].dtype))
+    every = group.scratch("many_totals", group.world * k * es, torch.uint8, dev)
+    dist.all_gather_into_tensor(every, mine, group=group.group)
+    outs = []
     if group.rank > 0:
-        # inclusive scan of the G totals; the carry into shard r is entry r-1
-        init = local.scan_(ops.identity, op, torch.empty_like(totals), totals)[group.rank - 1: group.rank]
-    return local.scan_(f, op, dst, src, init=init, tmp=tmp)
+        # [rank][job] -> [job][rank]: each job's totals become one contiguous run
+        by_job = every.view(group.world, k, es)[: group.rank].permute(1, 0, 2).contiguous()
+    for i, j in enumerate(jobs):
+        init = by_job[i].reshape(-1).view(j[2].dtype) if group.rank > 0 else None
+        outs.append(local.scan_(ops.identity, j[0], j[1], j[2], init=init, tmp=j[3] if len(j) > 3 else None))
+    return outs
 
 
 # ---- sample sort ---------------------------------------------------------------------------------

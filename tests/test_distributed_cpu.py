@@ -28,9 +28,12 @@ class HostOps:
         self.kfd, self.O = kfd, O
         self.opc = {"+": 0, "*": 1, "min": 2, "max": 3}
 
-    def reduce(self, f, op, x):
-        v = self.O.c_mapreduce(0, self.opc[op], x.numpy())
-        return torch.tensor([v], dtype=x.dtype)
+    def reduce(self, f, op, x, out=None):
+        v = torch.tensor([self.O.c_mapreduce(0, self.opc[op], x.numpy())], dtype=x.dtype)
+        if out is None:
+            return v
+        out.copy_(v)
+        return out
 
     def fold(self, op, partials, g=None):
         return self.reduce(None, op, partials)
@@ -42,7 +45,11 @@ class HostOps:
                 a, b = src[0].numpy(), src[1].numpy()
             else:
                 a, b = src[:, 0].contiguous().numpy(), src[:, 1].contiguous().numpy()
-            oa, ob = self.O.c_scan_affine(a, b, init=None if init is None else init.double().numpy())
+            seed = None
+            if init is not None:  # (a, b) pairs of the shards before this one, folded left to right
+                pa, pb = self.O.c_scan_affine(init[0::2].contiguous().numpy(), init[1::2].contiguous().numpy())
+                seed = np.array([pa[-1], pb[-1]])
+            oa, ob = self.O.c_scan_affine(a, b, init=seed)
             if isinstance(dst, (tuple, list)):
                 dst[0].copy_(torch.from_numpy(oa).float())
                 dst[1].copy_(torch.from_numpy(ob).float())
@@ -50,7 +57,10 @@ class HostOps:
                 dst[:, 0] = torch.from_numpy(oa).float()
                 dst[:, 1] = torch.from_numpy(ob).float()
             return dst
-        out = self.O.c_scan(0, self.opc[op], src.numpy(), init=None if init is None else init.numpy()[0])
+        seed = None
+        if init is not None:  # totals of the shards before this one, folded left to right
+            seed = self.O.c_scan(0, self.opc[op], init.numpy())[-1]
+        out = self.O.c_scan(0, self.opc[op], src.numpy(), init=seed)
         dst.copy_(torch.from_numpy(np.asarray(out)).to(dst.dtype))
         return dst
 
@@ -99,6 +109,12 @@ def _worker(rank, world, port, n_per, tmpdir):
         dst = torch.empty(n_per, dtype=torch.int32)
         kfd.scan_(group, "+", dst, torch.from_numpy(gu[lo:hi]), local=host)
         assert (dst.numpy() == np.cumsum(gu, dtype=np.int32)[lo:hi]).all()
+        # two arrays of one element size with one exchange: wrapping + over Int32 and min over Float32
+        gf = rng.random(n).astype(np.float32)
+        d1, d2 = torch.empty(n_per, dtype=torch.int32), torch.empty(n_per, dtype=torch.float32)
+        kfd.scan_many_(group, [("+", d1, torch.from_numpy(gu[lo:hi])), ("min", d2, torch.from_numpy(gf[lo:hi]))], local=host)
+        assert (d1.numpy() == np.cumsum(gu, dtype=np.int32)[lo:hi]).all()
+        assert (d2.numpy() == np.minimum.accumulate(gf)[lo:hi]).all()
 
         a = (0.5 + 0.5 * rng.random(n)).astype(np.float32)
         b = (2 * rng.random(n) - 1).astype(np.float32)
