@@ -7,9 +7,11 @@
 # src/scan/scan.jl:218-284,414-479, src/sort/sort1d.jl:307-502,780-874,1006-1090 and
 # src/allocations.jl:16-49 of KernelForge.jl v0.2.0.
 #
-# The operator set is fixed: identity/abs2/abs as `f`, + * min max & | xor as `op`, identity/sqrt as
-# `g`, plus `AffineCompose()` for scans. Any other closure, `by`, `lt`, `rev`, a custom `uint_map`
-# or `dims` raises `ArgumentError`; there is no fallback path of any kind.
+# The operator set is fixed: identity/abs2/abs as `f` (over tuples of arrays: `*`, `SqDiff()`,
+# `WeightedSq()`), + * min max & | xor as `op`, identity/sqrt as `g`, plus `AffineCompose()` for scans.
+# Any other closure, `by`, `lt`, `rev`, a custom `uint_map` or `dims` raises `ArgumentError`; there is
+# no fallback path of any kind. Also here: argmax / argmin / findfirst / findlast / vcopy! / setvalue!
+# (src/search/highlevel.jl:1-52, src/copy/copy.jl:24-56), with Julia's 1-based indices.
 #
 # This file cannot be executed where it was written (no Julia toolchain); its executable twin is the
 # Python package next to it, which binds the same C entry points with the same argument order.
@@ -63,7 +65,7 @@ cfg_ptr(r::Ref{LaunchCfg}) = Base.unsafe_convert(Ptr{LaunchCfg}, r)
 function check(code::Cint, what)
     code == KF_OK && return nothing
     msg = unsafe_string(ccall((:kf_error_string, libkf), Cstring, (Cint,), code))
-    code in (1, 2, 6) ? throw(ArgumentError("$what: $msg")) : error("$what: $msg")
+    code in (1, 2, 6, 7) ? throw(ArgumentError("$what: $msg")) : error("$what: $msg")
 end
 
 stream_handle() = reinterpret(Ptr{Cvoid}, CUDA.stream().handle)
@@ -149,8 +151,45 @@ function mapreduce(f, op, src::CuArray{T}; g=identity, to_cpu::Bool=true, kwargs
     mapreduce!(f, op, dst, src; g, kwargs...)
     to_cpu ? Array(dst)[1] : dst   # the only host<->device crossing, as in mapreduce1d.jl:203
 end
-mapreduce(f, op, srcs::Tuple; kwargs...) =
-    length(srcs) == 1 ? mapreduce(f, op, srcs[1]; kwargs...) : throw(ArgumentError("multi-array mapreduce is not implemented"))
+
+# Tuple form mapreduce(f, op, (x, y, ...)) (src/mapreduce/1D/mapreduce1d.jl:186-204): f is one of `*`
+# (product of 2 to 4 arrays; the dot product for two), SqDiff() ((x - y)^2) or WeightedSq() (w * x^2).
+"(x, y) -> (x - y)^2 over a pair of arrays"
+struct SqDiff <: Function end
+(::SqDiff)(x, y) = (x - y)^2
+"(w, x) -> w * x^2 over a pair of arrays"
+struct WeightedSq <: Function end
+(::WeightedSq)(w, x) = w * x * x
+mapn_code(::typeof(*)) = Cint(0)
+mapn_code(::SqDiff) = Cint(1)
+mapn_code(::WeightedSq) = Cint(2)
+mapn_code(f) = throw(ArgumentError("unsupported map over a tuple of arrays $f: this library implements *, SqDiff() and WeightedSq()"))
+
+function mapreduce!(f, op, dst::CuArray{T}, srcs::NTuple{N,CuArray{T}}; dims=nothing, g=identity, tmp=nothing, Nitem=nothing,
+                    workgroup=nothing, blocks=nothing, arch=nothing) where {T,N}
+    N == 1 && return mapreduce!(f, op, dst, srcs[1]; dims, g, tmp, Nitem, workgroup, blocks, arch)
+    (dims === nothing || dims === Colon()) || throw(ArgumentError("only full reductions (dims=nothing) are implemented"))
+    2 <= N <= 4 || throw(ArgumentError("the tuple form takes 2 to 4 arrays"))
+    n = length(srcs[1])
+    all(x -> length(x) == n, srcs) || throw(ArgumentError("the arrays of the tuple form must have equal lengths"))
+    n == 0 && throw(ArgumentError("reducing over an empty collection is not allowed"))
+    cfg = make_cfg(workgroup, Nitem, blocks)
+    buf = _resolve_tmp(tmp, mapreduce_bytes(T, n, cfg))
+    ws = buf.arrays.workspace
+    ptrs = CuPtr{Cvoid}[pointer(x) for x in srcs]   # host array of device pointers
+    GC.@preserve cfg ptrs begin
+        check(ccall((:kf_mapreduce_multi, libkf), Cint,
+                    (Cint, Cint, Cint, Cint, Ptr{CuPtr{Cvoid}}, Cint, UInt64, CuPtr{Cvoid}, CuPtr{Cvoid}, Csize_t, Ptr{LaunchCfg}, Ptr{Cvoid}),
+                    mapn_code(f), op_code(op), post_code(g), dtype_code(T), ptrs, N, n, pointer(dst), pointer(ws), length(ws),
+                    cfg_ptr(cfg), stream_handle()), "mapreduce!")
+    end
+    dst
+end
+function mapreduce(f, op, srcs::NTuple{N,CuArray{T}}; g=identity, to_cpu::Bool=true, kwargs...) where {T,N}
+    dst = CUDA.zeros(T, 1)
+    mapreduce!(f, op, dst, srcs; g, kwargs...)
+    to_cpu ? Array(dst)[1] : dst
+end
 const mapreduce1d = mapreduce
 const mapreduce1d! = mapreduce!
 
@@ -158,7 +197,9 @@ const mapreduce1d! = mapreduce!
 scan!(op, dst, src; kwargs...) = scan!(identity, op, dst, src; kwargs...)
 function scan!(f, op, dst::CuArray{T}, src::CuArray{T}; g=identity, tmp=nothing, Nitem=nothing, workgroup=nothing,
                family=nothing, arch=nothing, init=nothing) where {T}
-    g === identity || throw(ArgumentError("scan supports g=identity only"))
+    # g is applied to every output element (src/scan/scan_kernel.jl:463,470,474); `init` is a device
+    # array whose elements are folded left to right and seed the scan (one element, or the totals of
+    # the shards before this one in a sharded scan)
     n = length(src)
     n == 0 && return dst
     length(dst) == n || throw(ArgumentError("dst and src must have equal lengths"))
@@ -167,9 +208,11 @@ function scan!(f, op, dst::CuArray{T}, src::CuArray{T}; g=identity, tmp=nothing,
     ws = buf.arrays.workspace
     GC.@preserve cfg begin
         check(ccall((:kf_scan, libkf), Cint,
-                    (Cint, Cint, Cint, CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, CuPtr{Cvoid}, CuPtr{Cvoid}, Csize_t, Ptr{LaunchCfg}, Ptr{Cvoid}),
-                    map_code(f), op_code(op), dtype_code(T), pointer(src), pointer(dst), n,
-                    init === nothing ? CU_NULL : pointer(init), pointer(ws), length(ws), cfg_ptr(cfg), stream_handle()), "scan!")
+                    (Cint, Cint, Cint, Cint, CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, CuPtr{Cvoid}, UInt32, CuPtr{Cvoid}, Csize_t,
+                     Ptr{LaunchCfg}, Ptr{Cvoid}),
+                    map_code(f), op_code(op), post_code(g), dtype_code(T), pointer(src), pointer(dst), n,
+                    init === nothing ? CU_NULL : pointer(init), init === nothing ? 0 : length(init),
+                    pointer(ws), length(ws), cfg_ptr(cfg), stream_handle()), "scan!")
     end
     dst
 end
@@ -184,10 +227,11 @@ function scan!(f, op::AffineCompose, dst::NTuple{2,CuArray{Float32}}, src::NTupl
     ws = buf.arrays.workspace
     GC.@preserve cfg begin
         check(ccall((:kf_scan_affine_soa, libkf), Cint,
-                    (CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt64, CuPtr{Cfloat}, CuPtr{Cvoid}, Csize_t,
+                    (CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt64, CuPtr{Cfloat}, UInt32, CuPtr{Cvoid}, Csize_t,
                      Ptr{LaunchCfg}, Ptr{Cvoid}),
                     pointer(src[1]), pointer(src[2]), pointer(dst[1]), pointer(dst[2]), n,
-                    init === nothing ? CU_NULL : pointer(init), pointer(ws), length(ws), cfg_ptr(cfg), stream_handle()), "scan!")
+                    init === nothing ? CU_NULL : pointer(init), init === nothing ? 0 : length(init) ÷ 2,
+                    pointer(ws), length(ws), cfg_ptr(cfg), stream_handle()), "scan!")
     end
     dst
 end
@@ -201,9 +245,9 @@ function scan!(f, op::AffineCompose, dst::CuArray{NTuple{2,Float32}}, src::CuArr
     ws = buf.arrays.workspace
     GC.@preserve cfg begin
         check(ccall((:kf_scan_affine_aos, libkf), Cint,
-                    (CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, CuPtr{Cfloat}, CuPtr{Cvoid}, Csize_t, Ptr{LaunchCfg}, Ptr{Cvoid}),
-                    pointer(src), pointer(dst), n, init === nothing ? CU_NULL : pointer(init), pointer(ws), length(ws),
-                    cfg_ptr(cfg), stream_handle()), "scan!")
+                    (CuPtr{Cfloat}, CuPtr{Cfloat}, UInt64, CuPtr{Cfloat}, UInt32, CuPtr{Cvoid}, Csize_t, Ptr{LaunchCfg}, Ptr{Cvoid}),
+                    pointer(src), pointer(dst), n, init === nothing ? CU_NULL : pointer(init),
+                    init === nothing ? 0 : length(init) ÷ 2, pointer(ws), length(ws), cfg_ptr(cfg), stream_handle()), "scan!")
     end
     dst
 end
@@ -262,6 +306,116 @@ function sortperm(keys::CuArray; kwargs...)
     check(ccall((:kf_iota, libkf), Cint, (Cint, CuPtr{Cvoid}, UInt64, UInt64, Ptr{Cvoid}),
                 dtype_code(eltype(idx)), pointer(idx), n, 1, stream_handle()), "sortperm")
     first(sort!(similar(idx), idx; keys, keys_dst=similar(keys), kwargs...))
+end
+
+# ---- search, copy, fill (src/search/highlevel.jl:1-52, src/copy/copy.jl:24-56) ------------------------
+argmax_bytes(::Type{T}, n) where {T} =
+    ccall((:kf_argmax_workspace_bytes, libkf), Csize_t, (Cint, UInt64), dtype_code(T), n)
+
+"(value, index) of the first extremal f(src[i]) under `rel` (`>` or `<`); ties go to the smallest index. 1-based."
+function argmax1d(f, rel, src::CuArray{T}; tmp=nothing) where {T}
+    greater = rel === (>) ? Cint(1) : rel === (<) ? Cint(0) : throw(ArgumentError("unsupported relation $rel: argmax takes > or <"))
+    n = length(src)
+    n == 0 && throw(ArgumentError("argmax over an empty collection is not allowed"))
+    ws = tmp === nothing ? CUDA.zeros(UInt8, argmax_bytes(T, n)) : tmp
+    val = CuArray{T}(undef, 1)
+    idx = CuArray{UInt64}(undef, 1)
+    check(ccall((:kf_argmax, libkf), Cint,
+                (Cint, Cint, Cint, CuPtr{Cvoid}, UInt64, CuPtr{Cvoid}, CuPtr{UInt64}, CuPtr{Cvoid}, Csize_t, Ptr{Cvoid}),
+                map_code(f), greater, dtype_code(T), pointer(src), n, pointer(val), pointer(idx), pointer(ws), length(ws),
+                stream_handle()), "argmax")
+    (Array(val)[1], Int(Array(idx)[1]) + 1)
+end
+argmax(src::CuArray) = argmax1d(identity, >, src)[2]
+argmax(rel, src::CuArray) = argmax1d(identity, rel, src)[2]
+argmin(src::CuArray) = argmax1d(identity, <, src)[2]
+
+# Predicates are Base's partially applied comparisons: >(v), <(v), >=(v), <=(v), ==(v), !=(v).
+pred_code(p::Base.Fix2{typeof(>)}) = (Cint(0), p.x)
+pred_code(p::Base.Fix2{typeof(<)}) = (Cint(1), p.x)
+pred_code(p::Base.Fix2{typeof(>=)}) = (Cint(2), p.x)
+pred_code(p::Base.Fix2{typeof(<=)}) = (Cint(3), p.x)
+pred_code(p::Base.Fix2{typeof(==)}) = (Cint(4), p.x)
+pred_code(p::Base.Fix2{typeof(!=)}) = (Cint(5), p.x)
+pred_code(p) = throw(ArgumentError("unsupported predicate $p: use >(v), <(v), >=(v), <=(v), ==(v) or !=(v)"))
+
+function _find(pred, src::CuArray{T}, last::Bool) where {T}
+    code, v = pred_code(pred)
+    operand = Ref(convert(T, v))           # host scalar
+    out = CuArray{UInt64}(undef, 1)
+    n = length(src)
+    GC.@preserve operand begin
+        check(ccall((:kf_find, libkf), Cint,
+                    (Cint, Cint, Cint, CuPtr{Cvoid}, UInt64, Ptr{Cvoid}, CuPtr{UInt64}, Ptr{Cvoid}),
+                    code, Cint(last), dtype_code(T), pointer(src), n, operand, pointer(out), stream_handle()), "findfirst")
+    end
+    r = Array(out)[1]
+    last ? (r == 0 ? nothing : Int(r)) : (r >= n ? nothing : Int(r) + 1)   # C side: 0-based / index + 1
+end
+findfirst(pred, src::CuArray) = _find(pred, src, false)
+findlast(pred, src::CuArray) = _find(pred, src, true)
+
+"Vectorised device copy (src/copy/copy.jl:24-28)."
+function vcopy!(dst::CuArray{T}, src::CuArray{T}) where {T}
+    length(dst) == length(src) || throw(ArgumentError("dst and src must have the same length"))
+    check(ccall((:kf_vcopy, libkf), Cint, (CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, Ptr{Cvoid}),
+                pointer(dst), pointer(src), sizeof(T) * length(src), stream_handle()), "vcopy!")
+    dst
+end
+"Vectorised fill (src/copy/copy.jl:30-55)."
+function setvalue!(dst::CuArray{T}, val) where {T}
+    v = Ref(convert(T, val))
+    GC.@preserve v begin
+        check(ccall((:kf_setvalue, libkf), Cint, (Cint, CuPtr{Cvoid}, UInt64, Ptr{Cvoid}, Ptr{Cvoid}),
+                    dtype_code(T), pointer(dst), length(dst), v, stream_handle()), "setvalue!")
+    end
+    dst
+end
+
+# ---- scan without a workspace (no counterpart in KernelForge.jl) -----------------------------------------
+# For callers that cannot allocate device memory where they call: the descriptors live in a fixed 1 MiB
+# device array of the library. Calls on one device must not overlap; the first call per device should
+# come before any stream capture.
+function scan_static!(f, op, dst::CuArray{T}, src::CuArray{T}; g=identity, init=nothing) where {T}
+    n = length(src)
+    length(dst) == n || throw(ArgumentError("dst and src must have equal lengths"))
+    check(ccall((:kf_scan_static, libkf), Cint,
+                (Cint, Cint, Cint, Cint, CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, CuPtr{Cvoid}, UInt32, Ptr{Cvoid}),
+                map_code(f), op_code(op), post_code(g), dtype_code(T), pointer(src), pointer(dst), n,
+                init === nothing ? CU_NULL : pointer(init), init === nothing ? 0 : length(init), stream_handle()), "scan_static!")
+    dst
+end
+scan_static_max_n(::Type{T}) where {T} = ccall((:kf_scan_static_max_n, libkf), UInt64, (Cint,), dtype_code(T))
+scan_static_check() = ccall((:kf_scan_static_check, libkf), Cint, (Ptr{Cvoid},), stream_handle())
+
+# ---- helpers of a sharded sample sort (no counterpart in KernelForge.jl) ---------------------------------
+"For each splitter, the index (0-based count) of the first element of the sorted `keys` that is greater."
+function upper_bounds(keys::CuArray{K}, splitters::CuArray{K}) where {K}
+    out = CuArray{UInt64}(undef, length(splitters))
+    check(ccall((:kf_upper_bounds, libkf), Cint, (Cint, CuPtr{Cvoid}, UInt64, CuPtr{Cvoid}, Cint, CuPtr{UInt64}, Ptr{Cvoid}),
+                dtype_code(K), pointer(keys), length(keys), pointer(splitters), length(splitters), pointer(out), stream_handle()),
+          "upper_bounds")
+    out
+end
+"Destination piece (UInt8) of every key: the number of splitters below it in the sort's key order."
+function bucket_ids(keys::CuArray{K}, splitters::CuArray{K}) where {K}
+    out = CuArray{UInt8}(undef, length(keys))
+    check(ccall((:kf_bucket_ids, libkf), Cint, (Cint, CuPtr{Cvoid}, UInt64, CuPtr{Cvoid}, Cint, CuPtr{UInt8}, Ptr{Cvoid}),
+                dtype_code(K), pointer(keys), length(keys), pointer(splitters), length(splitters), pointer(out), stream_handle()),
+          "bucket_ids")
+    out
+end
+
+# ---- library -------------------------------------------------------------------------------------------
+launch_count() = ccall((:kf_launch_count, libkf), UInt64, ())
+num_sms() = Int(ccall((:kf_num_sms, libkf), Cint, ()))
+last_cuda_error() = ccall((:kf_last_cuda_error, libkf), Cint, ())
+abi_version() = ccall((:kf_abi_version, libkf), Cint, ())
+function launch_table_lookup(primitive::Integer, elem_bytes::Integer, n::Integer)
+    out = Ref(LaunchCfg(0, 0, 0, 0))
+    check(ccall((:kf_launch_table_lookup, libkf), Cint, (Cint, Cint, UInt64, Ptr{LaunchCfg}), primitive, elem_bytes, n, out),
+          "launch_table_lookup")
+    out[]
 end
 
 "Device-side status of a workspace after synchronising the stream (KF_ERR_TIMEOUT if a bounded wait ran out)."

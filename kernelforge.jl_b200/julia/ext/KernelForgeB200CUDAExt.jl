@@ -10,7 +10,7 @@ import ..KernelForgeB200: KernelBuffer, libkf
 function __init__()
     CUDA.functional() || return
     v = ccall((:kf_abi_version, libkf), Cint, ())
-    v == 1 || error("libkf_b200.so has ABI version $v, expected 1")
+    v == 2 || error("libkf_b200.so has ABI version $v, expected 2")
     for dev in CUDA.devices()
         cap = CUDA.capability(dev)
         cap >= v"10.0" || @warn "libkf_b200.so is built for sm_100a only; device $(CUDA.name(dev)) is $(cap)"
