@@ -46,7 +46,7 @@ def workload_config(world):
     n = N_HEADLINE
     return {"workload": "inclusive scan!(+, dst, x): Float32 x~U[0,1) n=2^28 and UInt32 x~U{0..255} n=2^28 "
                         "per GPU" + ("" if world == 1 else "; sharded over %d GPUs (global n=%d*2^28): local "
-                                     "reduce, one NCCL allgather of the shard totals, seeded local scan" % (world, world)),
+                                     "reduce, NCCL allgather of the shard totals, seeded local scan" % (world, world)),
             "n_per_gpu": n, "algorithmic_bytes_per_step": world * 2 * 8 * n,
             "l2": "inputs (1 GiB per array) are larger than the 126 MB L2; no flush needed"}
 
@@ -344,7 +344,7 @@ def run_case(args):
     from __graft_entry__ import load_package
     kf = load_package()
     torch.cuda.set_device(0)
-    n = 1 << args.log2n
+    n = args.n if args.n else 1 << args.log2n
     g = torch.Generator(device="cuda").manual_seed(0)
     case = args.case
     if case in ("scan_u32", "scan_f32", "scan_f64", "scan_u8", "mapreduce_f32"):
@@ -368,9 +368,13 @@ def run_case(args):
         da, db = torch.empty_like(a), torch.empty_like(b)
         tmp = kf.get_allocation(kf.Scan1D, kf.identity, kf.AffineCompose(), (a, b))
         fn, nbytes = (lambda: kf.scan_(kf.AffineCompose(), (da, db), (a, b), tmp=tmp)), 16 * n
-    elif case in ("sort_u32", "sort_f32", "sort_pairs"):
-        keys = (torch.randn(n, dtype=torch.float32, device="cuda", generator=g) if case == "sort_f32" else
-                torch.randint(0, 1 << 32, (n,), dtype=torch.int64, device="cuda", generator=g).to(torch.int32).view(torch.uint32))
+    elif case in ("sort_u32", "sort_f32", "sort_pairs", "sort_u64"):
+        if case == "sort_f32":
+            keys = torch.randn(n, dtype=torch.float32, device="cuda", generator=g)
+        elif case == "sort_u64":
+            keys = torch.randint(-2**63, 2**63 - 1, (n,), dtype=torch.int64, device="cuda", generator=g).view(torch.uint64)
+        else:
+            keys = torch.randint(0, 1 << 32, (n,), dtype=torch.int64, device="cuda", generator=g).to(torch.int32).view(torch.uint32)
         out = torch.empty_like(keys)
         if case == "sort_pairs":
             idx = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
@@ -379,7 +383,7 @@ def run_case(args):
             fn, nbytes = (lambda: kf.sort_(vout, idx, keys=keys, keys_dst=out, tmp=tmp)), 68 * n
         else:
             tmp = kf.get_allocation(kf.Sort1D, keys)
-            fn, nbytes = (lambda: kf.sort_(out, keys, tmp=tmp)), 36 * n
+            fn, nbytes = (lambda: kf.sort_(out, keys, tmp=tmp)), (136 if case == "sort_u64" else 36) * n
     else:
         raise SystemExit("unknown --case %r" % case)
     fn()
@@ -621,7 +625,7 @@ def run_gpu_arm(args):
         if world == 1:
             kf.scan_("+", df, xf, tmp=tmp_f)
             kf.scan_("+", du, xu, tmp=tmp_u)
-        else:  # both arrays with one exchange: 2 reductions, one allgather, 2 seeded scans
+        else:  # 2 reductions, 2 seeded scans; each array's allgather runs behind the other array's kernels
             kfd.scan_many_(group, [("+", df, xf, tmp_f), ("+", du, xu, tmp_u)])
 
     def barrier():
@@ -814,7 +818,7 @@ def run_gpu_arm(args):
             "config": workload_config(world),
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches,
             "gpu_launches_how": "kf_launch_count() of libkf_b200.so before and after the timed region on rank 0 (%s per step)"
-                                % ("2 scan kernels" if world == 1 else "2 reductions + 2 seeded scans; the allgather is NCCL's"),
+                                % ("2 scan kernels" if world == 1 else "2 reductions + 2 seeded scans; the allgathers are NCCL's"),
             "clocks": clocks, "burst": burst,
         }
         if world == 1:
@@ -843,8 +847,9 @@ def main():
     ap.add_argument("--detail", type=int, default=1, help="1: also measure the other primitives (single GPU)")
     ap.add_argument("--case", default=None,
                     help="run ONE primitive a few times at n=2^log2n and exit (small case for profiler captures): "
-                         "scan_u32, scan_f32, scan_f64, scan_u8, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_pairs")
+                         "scan_u32, scan_f32, scan_f64, scan_u8, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_u64, sort_pairs")
     ap.add_argument("--log2n", type=int, default=26)
+    ap.add_argument("--n", type=int, default=0, help="with --case: an exact element count instead of 2^log2n")
     ap.add_argument("--sharded", action="store_true",
                     help="measure the sharded configuration instead (mapreduce, scan and sample sort over one global "
                          "array of 2^--global-log2n elements split across the ranks; strong scaling)")

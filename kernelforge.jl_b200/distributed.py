@@ -9,7 +9,7 @@ rank owns one contiguous shard of a global array (rank order = array order) and 
   scan      : local reduce -> allgather of the shard totals -> local scan seeded with the totals of
               the shards before it, which the scan kernel folds itself in rank order (12n bytes
               instead of the 16n of "scan, then fix up", and no kernel for the carry). `scan_many_`
-              does this for several arrays with ONE allgather. Non-commutative operators
+              does this for several arrays with the allgathers running behind the local kernels. Non-commutative operators
               (AffineCompose) take the ordered route: local scan for the total, then the seeded scan.
   sort      : samples of the shard, allgather, identical splitter choice everywhere -> cut the shard
               into one run per destination -> all-to-all of the runs (NCCL, over NVLink) -> local
@@ -190,27 +190,28 @@ def scan_(group: ShardGroup, *args, tmp=None, g=ops.identity, local: LocalOps = 
 
 
 def scan_many_(group: ShardGroup, jobs, *, local: LocalOps = _DEFAULT_OPS):
-    """Several sharded scans with ONE exchange: `jobs` are (op, dst, src) or (op, dst, src, tmp) tuples of
-    commutative-or-not elementwise operators on arrays whose elements have the same size (AffineCompose
-    goes through `scan_`). All local reductions first, one allgather of every job's shard total, then
-    the seeded scans."""
+    """Several sharded scans whose exchanges hide behind the local kernels: `jobs` are (op, dst, src) or
+    (op, dst, src, tmp) tuples with elementwise operators (AffineCompose goes through `scan_`).
+    Order of work: reduce job 0, start its allgather (asynchronously, on the communication stream),
+    reduce job 1, start its allgather, ..., then for each job wait for its totals and run the seeded
+    scan. The allgather of job i runs while job i+1 is reduced (or job i-1 is scanned), so what a step
+    exposes of the exchange is close to nothing instead of one latency per array."""
     if group.world == 1:
         return [local.scan_(ops.identity, j[0], j[1], j[2], tmp=j[3] if len(j) > 3 else None) for j in jobs]
-    first = jobs[0][2]
-    es, dev, k = first.element_size(), first.device, len(jobs)
-    if any(isinstance(j[0], ops.AffineCompose) or j[2].element_size() != es for j in jobs):
-        raise C.ArgumentError("scan_many_ takes elementwise operators on arrays of one element size")
-    mine = group.scratch("many_partials", k * es, torch.uint8, dev)
+    if any(isinstance(j[0], ops.AffineCompose) for j in jobs):
+        raise C.ArgumentError("scan_many_ takes elementwise operators; use scan_ for AffineCompose")
+    pending = []
     for i, j in enumerate(jobs):
-        local.reduce(ops.identity, j[0], j[2], out=mine[i * es:(i + 1) * es].view(j[2].dtype))
-    every = group.scratch("many_totals", group.world * k * es, torch.uint8, dev)
-    dist.all_gather_into_tensor(every, mine, group=group.group)
+        src = j[2]
+        part = local.reduce(ops.identity, j[0], src, out=group.scratch("many_partial%d" % i, 1, src.dtype, src.device))
+        totals = group.scratch("many_totals%d" % i, group.world, src.dtype, src.device)
+        work = dist.all_gather_into_tensor(_wire_view(totals)[0], _wire_view(part)[0], group=group.group, async_op=True)
+        pending.append((work, totals))
     outs = []
-    if group.rank > 0:
-        # [rank][job] -> [job][rank]: each job's totals become one contiguous run
-        by_job = every.view(group.world, k, es)[: group.rank].permute(1, 0, 2).contiguous()
-    for i, j in enumerate(jobs):
-        init = by_job[i].reshape(-1).view(j[2].dtype) if group.rank > 0 else None
+    for (work, totals), j in zip(pending, jobs):
+        work.wait()
+        # the scan kernel folds the totals of the shards before this one itself (ninit = rank)
+        init = totals[: group.rank] if group.rank > 0 else None
         outs.append(local.scan_(ops.identity, j[0], j[1], j[2], init=init, tmp=j[3] if len(j) > 3 else None))
     return outs
 
