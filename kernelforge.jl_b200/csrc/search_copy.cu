@@ -7,7 +7,8 @@
 // Semantics follow KernelForge.jl: argmax1d (src/search/argmax.jl:8-86, kernel
 // src/search/argmax_kernel.jl:1-148: `rel` is a strict comparison, ties go to the smallest index),
 // findfirst / findlast (src/search/findfirst.jl:3-110), vcopy! / setvalue! (src/copy/copy.jl:1-55).
-// Indices are 0-based here; "not found" is n.
+// Indices are 0-based here. findfirst reports "not found" as UINT64_MAX; findlast stores found indices
+// as index + 1, so that 0 means "not found".
 #include "mapreduce_impl.cuh"
 
 namespace kf {
