@@ -220,14 +220,12 @@ def table_lookup(rows, prim, eb, nbytes):
     return None
 
 
-def cmd_choose(args):
-    with open(os.path.join(HERE, "launch_table.json")) as fh:
-        table = json.load(fh)
+def choose_rows(measurements, table_rows):
+    """The chooser as a pure function: `measurements` are the sweep's records (dicts), `table_rows` the
+    current table. Returns (new rows, report lines)."""
     meas = {}
-    with open(args.inp) as fh:
-        for line in fh:
-            r = json.loads(line)
-            meas.setdefault((r["primitive"], r["elem_bytes"]), {}).setdefault(r["log2n"], []).append(r)
+    for r in measurements:
+        meas.setdefault((r["primitive"], r["elem_bytes"]), {}).setdefault(r["log2n"], []).append(r)
     new_rows, report = [], []
     for (prim, eb), by_size in sorted(meas.items()):
         if prim == "scan_affine":
@@ -237,7 +235,7 @@ def cmd_choose(args):
         for log2n in sorted(by_size):
             cands = by_size[log2n]
             nbytes = (1 << log2n) * eb
-            cur = table_lookup(table["rows"], tprim, eb, nbytes)
+            cur = table_lookup(table_rows, tprim, eb, nbytes)
             cur_m = [c for c in cands if cur and c["threads"] == cur["threads"] and c["items"] == cur["items"] and
                      (prim != "mapreduce" or c["blocks_per_sm"] == max(cur["blocks_per_sm"], 1))]
             best = min(cands, key=lambda c: c["ms"])
@@ -264,6 +262,15 @@ def cmd_choose(args):
             new_rows.append({"primitive": tprim, "elem_bytes": eb, "max_bytes": max_bytes, "threads": t, "items": v,
                              "blocks_per_sm": per,
                              "from": "sweep cells %s w=%d, log2 n = %s" % (prim, eb, ",".join(str(s) for s in rg["sizes"]))})
+    return new_rows, report
+
+
+def cmd_choose(args):
+    with open(os.path.join(HERE, "launch_table.json")) as fh:
+        table = json.load(fh)
+    with open(args.inp) as fh:
+        measurements = [json.loads(line) for line in fh if line.strip()]
+    new_rows, report = choose_rows(measurements, table["rows"])
     print("| primitive | bytes | log2 n | table entry | ms | fastest | ms | gain of fastest | chosen |\n|---|---|---|---|---|---|---|---|---|")
     for r in report:
         print("| %s | %d | %d | %s | %.4f | %s | %.4f | %.1f %% | %s |" % (r[0], r[1], r[2], r[3], r[4], r[5], r[6], 100 * r[7], r[8]))

@@ -57,3 +57,61 @@ def test_names_follow_the_reference(kf):
     for name in ("mapreduce", "mapreduce_", "mapreduce1d", "mapreduce1d_", "scan", "scan_", "sort", "sort_",
                  "sortperm", "get_allocation", "KernelBuffer", "MapReduce1D", "Scan1D", "Sort1D", "AffineCompose"):
         assert hasattr(kf, name)
+
+
+def _load_autotune():
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("kf_autotune", os.path.join(root, "kernelforge.jl_b200", "tuning", "autotune.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_launch_table_chooser_rules():
+    """The rules the reference's autotuners use (data/tuning/sort/autotune.jl:143-147,236-253 and
+    data/tuning/mapreduce1d/autotune.jl:162-214): the current entry is a candidate, it is replaced only
+    by a win of more than 6 %, and regime boundaries lie at geometric midpoints of measured sizes."""
+    at = _load_autotune()
+    table = [{"primitive": "sort_keys", "elem_bytes": 0, "max_bytes": None, "threads": 512, "items": 16, "blocks_per_sm": 0}]
+
+    def rec(log2n, variant, t, v, ms):
+        return {"primitive": "sort_keys", "elem_bytes": 4, "log2n": log2n, "variant": variant, "threads": t, "items": v,
+                "blocks_per_sm": 0, "ms": ms}
+    meas = [rec(16, "512x16", 512, 16, 1.00), rec(16, "256x16", 256, 16, 0.80),   # 25 % faster: replaces the entry
+            rec(18, "512x16", 512, 16, 1.00), rec(18, "256x16", 256, 16, 0.96),   # 4 % faster: the entry stays
+            rec(20, "512x16", 512, 16, 1.00), rec(20, "512x24", 512, 24, 0.70)]
+    rows, report = at.choose_rows(meas, table)
+    assert [(r["threads"], r["items"]) for r in rows] == [(256, 16), (512, 16), (512, 24)]
+    assert rows[0]["max_bytes"] == int((2 ** 16 * 2 ** 18) ** 0.5) * 4   # geometric midpoint of 2^16 and 2^18 elements
+    assert rows[1]["max_bytes"] == int((2 ** 18 * 2 ** 20) ** 0.5) * 4 and rows[2]["max_bytes"] is None
+    assert all("log2 n" in r["from"] for r in rows)
+    assert [round(100 * r[7]) for r in report] == [25, 4, 43]
+
+
+def test_committed_launch_table_matches_the_header_and_the_sweep():
+    """launch_table.json and the generated header agree, and every measured row cites sweep cells that
+    exist in the committed measurements."""
+    import json
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tdir = os.path.join(root, "kernelforge.jl_b200", "tuning")
+    table = json.load(open(os.path.join(tdir, "launch_table.json")))
+    header = open(os.path.join(root, "kernelforge.jl_b200", "csrc", "launch_table.h")).read()
+    assert "kNumLaunchRows = %d" % len(table["rows"]) in header
+    cells = set()
+    for line in open(os.path.join(tdir, "sweep_b200.jsonl")):
+        r = json.loads(line)
+        cells.add((r["primitive"], r["elem_bytes"], r["log2n"]))
+    cited = 0
+    for row in table["rows"]:
+        m = re.match(r"sweep cells (\w+) w=(\d+), log2 n = ([\d,]+)", row.get("from", ""))
+        if not m:
+            assert row["elem_bytes"] == 0  # only the catch-all rows are not measured
+            continue
+        for l in m.group(3).split(","):
+            assert (m.group(1), int(m.group(2)), int(l)) in cells
+            cited += 1
+    assert cited >= 100
