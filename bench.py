@@ -503,6 +503,7 @@ def run_sharded(args):
                                 "frac_of_nominal_8TBs_x_gpus": round(b / ms_ / 1e6 / (NOMINAL_HBM_GBS * world), 4)}
                             for k, (b, ms_) in res.items()}}
         print(json.dumps(line))
+    group.close()
     dist.barrier()
     dist.destroy_process_group()
     return 0
@@ -833,6 +834,7 @@ def run_gpu_arm(args):
             line["primitives"] = prim
         print(json.dumps(line))
     if world > 1:
+        group.close()
         dist.barrier()
         dist.destroy_process_group()
     return 0

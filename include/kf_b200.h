@@ -287,6 +287,35 @@ int32_t kf_upper_bounds(int32_t key_dtype, const void *keys, uint64_t n,
 int32_t kf_bucket_ids(int32_t key_dtype, const void *keys, uint64_t n,
                       const void *splitters, int32_t nsplit, uint8_t *out, kf_stream_t stream);
 
+/* Peer-memory exchange of the sharded sample sort (one process per GPU on one node); the reference
+ * is single-device, so this group of entry points has no counterpart in the reference. A rank allocates ONE exchange buffer with
+ * kf_xbuf_alloc (a whole cudaMalloc allocation, which is what CUDA IPC shares; the only place where
+ * the library allocates device memory, at the caller's explicit request), exports it as 64 opaque
+ * bytes (kf_ipc_export), the other ranks map it (kf_ipc_open: enables peer access) and pull their runs
+ * out of it with kf_copy_d2d (one cudaMemcpyAsync per run, device-to-device over NVLink; remote data
+ * lands in local HBM before any kernel touches it). kf_ipc_close / kf_xbuf_free undo the two. */
+int32_t kf_xbuf_alloc(size_t nbytes, void **out);
+
+/* Frees a buffer of kf_xbuf_alloc (after every peer has closed its mapping). No counterpart in the
+ * reference. */
+int32_t kf_xbuf_free(void *ptr);
+
+/* The CUDA IPC handle of an exchange buffer as 64 opaque bytes, to be sent to the other ranks of the
+ * node by whatever channel the host layer has. No counterpart in the reference. */
+int32_t kf_ipc_export(const void *ptr, void *handle64);
+
+/* Maps a peer's exchange buffer into this process (and enables peer access to that GPU); `out` is a
+ * device pointer valid in this process. No counterpart in the reference. */
+int32_t kf_ipc_open(const void *handle64, void **out);
+
+/* Unmaps a buffer of kf_ipc_open. No counterpart in the reference. */
+int32_t kf_ipc_close(void *ptr);
+
+/* One asynchronous device-to-device copy (cudaMemcpyAsync) on `stream`; `src` may be a mapped peer
+ * buffer, in which case the bytes cross NVLink once and land in local memory. No counterpart in the
+ * reference. */
+int32_t kf_copy_d2d(void *dst, const void *src, uint64_t nbytes, kf_stream_t stream);
+
 /* ---- callers one step out: search, copy, fill ------------------------------------------------ */
 
 /* Comparison of an element with a scalar operand, for kf_find. */

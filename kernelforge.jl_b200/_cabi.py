@@ -80,6 +80,12 @@ PROTOTYPES = {
     "kf_find": (c_int32, [c_int32, c_int32, c_int32, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p]),
     "kf_vcopy": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p]),
     "kf_setvalue": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_void_p]),
+    "kf_xbuf_alloc": (c_int32, [c_size_t, POINTER(c_void_p)]),
+    "kf_xbuf_free": (c_int32, [c_void_p]),
+    "kf_ipc_export": (c_int32, [c_void_p, c_void_p]),
+    "kf_ipc_open": (c_int32, [c_void_p, POINTER(c_void_p)]),
+    "kf_ipc_close": (c_int32, [c_void_p]),
+    "kf_copy_d2d": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p]),
     "kf_bucket_ids": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_int32, c_void_p, c_void_p]),
 }
 

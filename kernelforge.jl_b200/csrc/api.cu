@@ -5,6 +5,7 @@
 #include "launch_table.h"
 
 #include <atomic>
+#include <string.h>
 
 namespace kf {
 
@@ -57,6 +58,52 @@ extern "C" int32_t kf_check(const void *ws, kf_stream_t stream) {
 }
 
 extern "C" uint64_t kf_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+// ---- peer-memory helpers of the sharded layer -------------------------------------------------------
+// A rank exports one device buffer (allocated here, so that it is a whole cudaMalloc allocation, which is
+// what CUDA IPC can share), the other ranks of the node map it and PULL their runs out of it with plain
+// device-to-device copies over NVLink. Nothing here is on the single-GPU path.
+extern "C" int32_t kf_xbuf_alloc(size_t nbytes, void **out) {
+    if (!out || nbytes == 0) return KF_ERR_INVALID_ARG;
+    KF_CUDA_TRY(cudaMalloc(out, nbytes));
+    return KF_OK;
+}
+
+extern "C" int32_t kf_xbuf_free(void *ptr) {
+    if (!ptr) return KF_OK;
+    KF_CUDA_TRY(cudaFree(ptr));
+    return KF_OK;
+}
+
+extern "C" int32_t kf_ipc_export(const void *ptr, void *handle64) {
+    if (!ptr || !handle64) return KF_ERR_INVALID_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 opaque bytes");
+    cudaIpcMemHandle_t h;
+    KF_CUDA_TRY(cudaIpcGetMemHandle(&h, const_cast<void *>(ptr)));
+    memcpy(handle64, &h, 64);
+    return KF_OK;
+}
+
+extern "C" int32_t kf_ipc_open(const void *handle64, void **out) {
+    if (!handle64 || !out) return KF_ERR_INVALID_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    KF_CUDA_TRY(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+    return KF_OK;
+}
+
+extern "C" int32_t kf_ipc_close(void *ptr) {
+    if (!ptr) return KF_OK;
+    KF_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return KF_OK;
+}
+
+extern "C" int32_t kf_copy_d2d(void *dst, const void *src, uint64_t nbytes, kf_stream_t stream) {
+    if (nbytes == 0) return KF_OK;
+    if (!dst || !src) return KF_ERR_INVALID_ARG;
+    KF_CUDA_TRY(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return KF_OK;
+}
 
 extern "C" int32_t kf_num_sms(void) { return device_sm_count(); }
 

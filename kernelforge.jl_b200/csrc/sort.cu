@@ -273,15 +273,70 @@ __global__ void __launch_bounds__(256) bucket_ids_kernel(const KeyT *keys, u64 n
     }
 }
 
+// The same for 16-byte aligned arrays: a thread takes 16 consecutive keys with 128-bit loads and writes
+// its 16 ids with one 128-bit store (one-byte stores made the scalar kernel issue-bound at a quarter of
+// the HBM rate).
+template <typename KeyT, bool IS_FLOAT>
+__global__ void __launch_bounds__(256) bucket_ids_vec_kernel(const KeyT *keys, u64 n16, const KeyT *splitters, int nsplit, uint8_t *out,
+                                                             bool sof) {
+    constexpr int KPV = 16 / sizeof(KeyT);  // keys per 16-byte vector
+    constexpr int NV = 16 / KPV;            // vectors per 16 keys
+    __shared__ KeyT s_split[256];
+    for (int j = threadIdx.x; j < nsplit; j += blockDim.x) s_split[j] = mapped_key<KeyT, IS_FLOAT>(splitters[j], sof);
+    __syncthreads();
+    const u64 stride = (u64)gridDim.x * blockDim.x;
+    for (u64 g = (u64)blockIdx.x * blockDim.x + threadIdx.x; g < n16; g += stride) {
+        uint4 v[NV];
+#pragma unroll
+        for (int q = 0; q < NV; ++q) v[q] = ld_stream_v4(reinterpret_cast<const uint4 *>(keys + g * 16) + q);
+        KeyT k[16];
+        memcpy(k, v, 16 * sizeof(KeyT));
+        uint8_t id[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const KeyT m = mapped_key<KeyT, IS_FLOAT>(k[e], sof);
+            int lo = 0, hi = nsplit;  // first splitter that is >= m
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (s_split[mid] < m) lo = mid + 1;
+                else hi = mid;
+            }
+            id[e] = (uint8_t)lo;
+        }
+        uint4 o;
+        memcpy(&o, id, 16);
+        st_stream_v4(out + g * 16, o);
+    }
+}
+
 template <typename KeyT>
 static void launch_bucket_ids(const KeyInfo &k, const void *keys, u64 n, const void *splitters, int nsplit, uint8_t *out, cudaStream_t s) {
-    u64 blocks = (n + 255) / 256;
+    const bool fl = k.is_float && sizeof(KeyT) >= 4;
+    u64 done = 0;
+    if ((((uintptr_t)keys | (uintptr_t)out) & 15u) == 0 && n >= 16) {
+        const u64 n16 = n / 16;
+        u64 blocks = (n16 + 255) / 256;
+        const u64 cap = (u64)device_sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+        if (fl)
+            bucket_ids_vec_kernel<KeyT, sizeof(KeyT) >= 4><<<(unsigned)blocks, 256, 0, s>>>((const KeyT *)keys, n16, (const KeyT *)splitters, nsplit, out, true);
+        else
+            bucket_ids_vec_kernel<KeyT, false><<<(unsigned)blocks, 256, 0, s>>>((const KeyT *)keys, n16, (const KeyT *)splitters, nsplit, out,
+                                                                                 k.signed_or_float);
+        note_launch();
+        done = n16 * 16;
+        if (done == n) return;
+    }
+    // scalar kernel: misaligned arrays, and the last n mod 16 keys
+    const KeyT *kp = (const KeyT *)keys + done;
+    const u64 rest = n - done;
+    u64 blocks = (rest + 255) / 256;
     const u64 cap = (u64)device_sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    if (k.is_float)
-        bucket_ids_kernel<KeyT, sizeof(KeyT) >= 4><<<(unsigned)blocks, 256, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out, true);
+    if (fl)
+        bucket_ids_kernel<KeyT, sizeof(KeyT) >= 4><<<(unsigned)blocks, 256, 0, s>>>(kp, rest, (const KeyT *)splitters, nsplit, out + done, true);
     else
-        bucket_ids_kernel<KeyT, false><<<(unsigned)blocks, 256, 0, s>>>((const KeyT *)keys, n, (const KeyT *)splitters, nsplit, out,
+        bucket_ids_kernel<KeyT, false><<<(unsigned)blocks, 256, 0, s>>>(kp, rest, (const KeyT *)splitters, nsplit, out + done,
                                                                          k.signed_or_float);
     note_launch();
 }

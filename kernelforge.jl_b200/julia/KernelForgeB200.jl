@@ -406,6 +406,27 @@ function bucket_ids(keys::CuArray{K}, splitters::CuArray{K}) where {K}
     out
 end
 
+# Peer-memory exchange of a sharded sample sort (one process per GPU): allocate / export / map / pull.
+function xbuf_alloc(nbytes::Integer)
+    out = Ref{CuPtr{Cvoid}}(CU_NULL)
+    check(ccall((:kf_xbuf_alloc, libkf), Cint, (Csize_t, Ptr{CuPtr{Cvoid}}), nbytes, out), "xbuf_alloc")
+    out[]
+end
+xbuf_free(p::CuPtr{Cvoid}) = check(ccall((:kf_xbuf_free, libkf), Cint, (CuPtr{Cvoid},), p), "xbuf_free")
+function ipc_export(p::CuPtr{Cvoid})
+    h = Vector{UInt8}(undef, 64)
+    check(ccall((:kf_ipc_export, libkf), Cint, (CuPtr{Cvoid}, Ptr{UInt8}), p, h), "ipc_export")
+    h
+end
+function ipc_open(h::Vector{UInt8})
+    out = Ref{CuPtr{Cvoid}}(CU_NULL)
+    check(ccall((:kf_ipc_open, libkf), Cint, (Ptr{UInt8}, Ptr{CuPtr{Cvoid}}), h, out), "ipc_open")
+    out[]
+end
+ipc_close(p::CuPtr{Cvoid}) = check(ccall((:kf_ipc_close, libkf), Cint, (CuPtr{Cvoid},), p), "ipc_close")
+copy_d2d(dst::CuPtr{Cvoid}, src::CuPtr{Cvoid}, nbytes::Integer) =
+    check(ccall((:kf_copy_d2d, libkf), Cint, (CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, Ptr{Cvoid}), dst, src, nbytes, stream_handle()), "copy_d2d")
+
 # ---- library -------------------------------------------------------------------------------------------
 launch_count() = ccall((:kf_launch_count, libkf), UInt64, ())
 num_sms() = Int(ccall((:kf_num_sms, libkf), Cint, ()))

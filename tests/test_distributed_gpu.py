@@ -76,6 +76,7 @@ def _worker(rank, world, port, n_per, tmpdir):
         off = sum(counts[:rank])
         assert (chunk.cpu().numpy() == np.sort(k16)[off:off + counts[rank]]).all()
         torch.cuda.synchronize()
+        group.close()
         with open(os.path.join(tmpdir, "ok%d" % rank), "w") as fh:
             fh.write("ok")
     finally:

@@ -335,3 +335,33 @@ def test_tens_of_millions_against_the_oracle(kf, oracle, n, kind):
     rng = np.random.default_rng(n)
     x = rand_keys(np.dtype(kind).type, n, rng)
     assert_same_bits(to_host(kf.sort(to_dev(x))), oracle.c_sort(x))
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.int16, np.uint32, np.int32, np.float32, np.uint64, np.float64])
+@pytest.mark.parametrize("n,offset", [(1, 0), (15, 0), (16, 0), (1000, 0), (100_003, 0), (100_003, 3), (1 << 20, 0)])
+def test_bucket_ids_and_upper_bounds(kf, oracle, dtype, n, offset):
+    """The two helpers of the sharded sample sort against numpy on the mapped keys: destination ids of an
+    unsorted shard (vector path, scalar tail, misaligned view) and the cut points of a sorted one."""
+    import ctypes
+    from kernelforge_jl_b200 import _cabi as C, ops
+    rng = np.random.default_rng(n + offset)
+    x = rand_keys(dtype, n, rng)
+    nsplit = 7
+    spl = np.sort(oracle.np_uint_map(rand_keys(dtype, nsplit, rng)))
+    # splitters are keys: map the sorted unsigned images back through the sort order of real keys
+    cand = rand_keys(dtype, 4096, rng)
+    cand = cand[np.argsort(oracle.np_uint_map(cand), kind="stable")]
+    splitters = cand[np.linspace(100, 4000, nsplit).astype(int)]
+    ms = oracle.np_uint_map(splitters)
+    dx, ds = to_dev(x, offset=offset), to_dev(splitters)
+    out = torch.empty(n, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rc = kf.lib.kf_bucket_ids(ops.dtype_code(dx), dx.data_ptr(), n, ds.data_ptr(), nsplit, out.data_ptr(), st)
+    assert rc == C.OK
+    want = np.searchsorted(ms, oracle.np_uint_map(x), side="left").astype(np.uint8)
+    assert (out.cpu().numpy() == want).all()
+    srt = oracle.c_sort(x)
+    dsrt = to_dev(srt)
+    cuts = torch.empty(nsplit, dtype=torch.int64, device="cuda")
+    assert kf.lib.kf_upper_bounds(ops.dtype_code(dsrt), dsrt.data_ptr(), n, ds.data_ptr(), nsplit, cuts.data_ptr(), st) == C.OK
+    assert (cuts.cpu().numpy() == np.searchsorted(oracle.np_uint_map(srt), ms, side="right")).all()
