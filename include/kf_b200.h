@@ -316,6 +316,25 @@ int32_t kf_ipc_close(void *ptr);
  * reference. */
 int32_t kf_copy_d2d(void *dst, const void *src, uint64_t nbytes, kf_stream_t stream);
 
+/* Bytes of the region behind kf_peer_allgather (allocate it with kf_xbuf_alloc, clear it once, export
+ * it with kf_ipc_export). No counterpart in the reference. */
+size_t kf_peer_region_bytes(void);
+
+/* Allgather of ONE element per rank over peer memory, as a kernel of this library: the exchange of the
+ * sharded mapreduce (partials) and scan (shard totals) without a communication library and without the
+ * host. `peers` is a DEVICE array of `world` pointers to every rank's region (mapped with kf_ipc_open;
+ * entry `rank` is `local_region` itself), `value` one element of `elem_bytes` (1, 2, 4 or 8: the 8-byte
+ * case also carries an affine (a, b) pair) in device memory, `out` receives the `world` elements in rank
+ * order. `epoch` is a counter that all ranks advance together, starting at 1 (never 0); at most 64
+ * ranks. The kernel stores its element into every region over NVLink and then waits, with a limit, for
+ * the other ranks' elements in its OWN region; if one does not arrive it records KF_ERR_TIMEOUT in
+ * `status_ws` (a 256-byte cleared workspace header, read with kf_check; word 1 = the missing rank) and
+ * returns. All ranks must call it once per epoch. No counterpart in the reference, which is
+ * single-device. */
+int32_t kf_peer_allgather(const void *peers, const void *local_region, int32_t world, int32_t rank, uint32_t epoch,
+                          const void *value, int32_t elem_bytes, void *out, void *status_ws,
+                          const kf_launch_cfg *cfg, kf_stream_t stream);
+
 /* ---- callers one step out: search, copy, fill ------------------------------------------------ */
 
 /* Comparison of an element with a scalar operand, for kf_find. */

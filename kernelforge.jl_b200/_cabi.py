@@ -86,6 +86,9 @@ PROTOTYPES = {
     "kf_ipc_open": (c_int32, [c_void_p, POINTER(c_void_p)]),
     "kf_ipc_close": (c_int32, [c_void_p]),
     "kf_copy_d2d": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p]),
+    "kf_peer_region_bytes": (c_size_t, []),
+    "kf_peer_allgather": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_uint32, c_void_p, c_int32, c_void_p, c_void_p,
+                                    POINTER(LaunchCfg), c_void_p]),
     "kf_bucket_ids": (c_int32, [c_int32, c_void_p, c_uint64, c_void_p, c_int32, c_void_p, c_void_p]),
 }
 

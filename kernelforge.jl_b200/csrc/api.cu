@@ -105,6 +105,79 @@ extern "C" int32_t kf_copy_d2d(void *dst, const void *src, uint64_t nbytes, kf_s
     return KF_OK;
 }
 
+// ---- one-element allgather over peer memory ------------------------------------------------------------
+// The exchange of the sharded mapreduce and scan: every rank contributes ONE element (a shard total).
+// Each rank owns a small region that all ranks of the node have mapped; entry (slot, rank) of a region
+// is two 64-bit words {epoch:32 | low half:32}, {epoch:32 | high half:32}, each of which validates itself
+// (a 64-bit store is atomic), so no fence or flag separates value and tag. The kernel writes this rank's
+// element into entry (slot, rank) of EVERY region with system-scope stores over NVLink, then waits, with a
+// limit, until all entries of its own region carry the epoch, and writes the elements out in rank order.
+// Remote data is only ever read from local memory. Slots rotate with the epoch; since every rank waits
+// for every other rank, no rank can run more than one exchange ahead, so a slot is never overwritten
+// before it has been read.
+namespace kf {
+constexpr int kPeerSlots = 4;
+constexpr int kPeerMaxWorld = 64;
+constexpr size_t kPeerRegionBytes = (size_t)kPeerSlots * kPeerMaxWorld * 16;
+
+__device__ __forceinline__ void st_relaxed_sys_u64(u64 *p, u64 v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ u64 ld_relaxed_sys_u64(const u64 *p) {
+    u64 v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kPeerMaxWorld) peer_allgather_kernel(u64 *const *peers, const u64 *local, int world, int rank,
+                                                                       u32 epoch, const void *value, int elem_bytes, void *out,
+                                                                       u32 *status, u32 spin_limit) {
+    const int q = (int)threadIdx.x;
+    if (q >= world) return;
+    const int slot = (int)(epoch % (u32)kPeerSlots);
+    u64 v = 0;
+    memcpy(&v, value, (size_t)elem_bytes);  // elem_bytes <= 8
+    const u64 tag = (u64)epoch << 32;
+    u64 *theirs = peers[q] + ((size_t)slot * kPeerMaxWorld + rank) * 2;
+    st_relaxed_sys_u64(theirs, tag | (v & 0xFFFFFFFFull));
+    st_relaxed_sys_u64(theirs + 1, tag | (v >> 32));
+    const u64 *mine = local + ((size_t)slot * kPeerMaxWorld + q) * 2;
+    u64 w0 = 0, w1 = 0;
+    bool ok = false;
+    for (u32 spins = 0; spins <= spin_limit; ++spins) {
+        w0 = ld_relaxed_sys_u64(mine);
+        w1 = ld_relaxed_sys_u64(mine + 1);
+        if ((w0 >> 32) == epoch && (w1 >> 32) == epoch) {
+            ok = true;
+            break;
+        }
+        if (spins > 16) __nanosleep(spins > 256 ? 512 : 64);
+    }
+    if (!ok) {
+        record_error(status, KF_ERR_TIMEOUT, (u32)q);  // word 1: the rank whose element never arrived
+        return;
+    }
+    const u64 got = (w0 & 0xFFFFFFFFull) | (w1 << 32);
+    memcpy(static_cast<char *>(out) + (size_t)q * elem_bytes, &got, (size_t)elem_bytes);
+}
+}  // namespace kf
+
+extern "C" size_t kf_peer_region_bytes(void) { return kPeerRegionBytes; }
+
+extern "C" int32_t kf_peer_allgather(const void *peers, const void *local_region, int32_t world, int32_t rank, uint32_t epoch,
+                                     const void *value, int32_t elem_bytes, void *out, void *status_ws,
+                                     const kf_launch_cfg *cfg, kf_stream_t stream) {
+    if (!peers || !local_region || !value || !out || !status_ws) return KF_ERR_INVALID_ARG;
+    if (world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world || epoch == 0) return KF_ERR_INVALID_ARG;
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8) return KF_ERR_UNSUPPORTED;
+    peer_allgather_kernel<<<1, kPeerMaxWorld, 0, (cudaStream_t)stream>>>(
+        (u64 *const *)peers, (const u64 *)local_region, world, rank, epoch, value, elem_bytes, out, (u32 *)status_ws,
+        test_spin_limit(cfg));
+    note_launch();
+    KF_CUDA_TRY(cudaGetLastError());
+    return KF_OK;
+}
+
 extern "C" int32_t kf_num_sms(void) { return device_sm_count(); }
 
 extern "C" int32_t kf_launch_table_lookup(int32_t primitive, int32_t elem_bytes, uint64_t n, kf_launch_cfg *out) {

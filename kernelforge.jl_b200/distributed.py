@@ -4,8 +4,10 @@ The reference has no multi-device layer; this one follows the plan the primitive
 rank owns one contiguous shard of a global array (rank order = array order) and each primitive is
 "local kernel(s) + ONE small exchange":
 
-  mapreduce : local mapreduce -> allreduce of one partial per rank (allgather + ordered fold for
-              the operators NCCL cannot reduce) -> g (on the host when the value goes there anyway).
+  mapreduce : local mapreduce -> the partials of all ranks -> fold in rank order -> g. On GPUs of one
+              node the partials travel through peer memory (kf_peer_allgather: every rank stores its
+              element into all ranks' mapped regions and waits, with a limit, for the others in its
+              own); otherwise an allreduce (allgather + ordered fold for operators NCCL cannot reduce).
   scan      : local reduce -> allgather of the shard totals -> local scan seeded with the totals of
               the shards before it, which the scan kernel folds itself in rank order (12n bytes
               instead of the 16n of "scan, then fix up", and no kernel for the carry). `scan_many_`
@@ -45,11 +47,78 @@ SAMPLES_PER_RANK = 1024
 class ShardGroup:
     """The ranks that share one sharded array (a torch.distributed process group)."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, peer_memory=None):
+        """`peer_memory`: exchange shard totals and sample-sort runs through mapped peer memory (GPU
+        ranks of one node) instead of the communication library. Default: on when the backend is NCCL."""
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self._scratch = {}
+        self.peer_memory = (dist.get_backend(group) == "nccl") if peer_memory is None else bool(peer_memory)
+        self._peer = None
+
+    # ---- one-element allgather over peer memory (kf_peer_allgather) -----------------------------------
+    def _peer_setup(self, device):
+        import ctypes
+        lib = C.load()
+        nbytes = int(lib.kf_peer_region_bytes())
+        with torch.cuda.device(device):
+            mine = ctypes.c_void_p()
+            C.check(lib.kf_xbuf_alloc(nbytes, ctypes.byref(mine)), "peer region")
+            _as_tensor(mine.value, nbytes, torch.uint8, device).zero_()
+            handle = (ctypes.c_ubyte * 64)()
+            C.check(lib.kf_ipc_export(mine, handle), "peer region export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=self.group)
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(mine.value)
+                    continue
+                raw = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                ptr = ctypes.c_void_p()
+                C.check(lib.kf_ipc_open(raw, ctypes.byref(ptr)), "peer region of rank %d" % r)
+                ptrs.append(ptr.value)
+            table = torch.tensor(ptrs, dtype=torch.int64, device=device)
+            status = torch.zeros(256, dtype=torch.uint8, device=device)
+            torch.cuda.synchronize()
+        dist.barrier(group=self.group)  # every region is cleared and mapped before anybody writes into one
+        self._peer = {"mine": mine.value, "ptrs": ptrs, "table": table, "status": status, "epoch": 0, "device": device}
+
+    def peer_allgather(self, value, out=None):
+        """`value`: one element (or a Float32 (a, b) pair) on the device. Returns the elements of all ranks
+        in rank order, gathered by a kernel of the library over peer memory: no NCCL call, no host
+        synchronisation. Every rank must call it in the same order (the epoch advances with each call)."""
+        if self._peer is None:
+            self._peer_setup(value.device)
+        p = self._peer
+        p["epoch"] = p["epoch"] % 0xFFFFFFFF + 1  # 1, 2, ..., never 0
+        nb = value.numel() * value.element_size()
+        if out is None:
+            out = torch.empty(self.world * value.numel(), dtype=value.dtype, device=value.device)
+        with torch.cuda.device(value.device):
+            rc = C.load().kf_peer_allgather(p["table"].data_ptr(), p["mine"], self.world, self.rank, p["epoch"], value.data_ptr(), nb,
+                                            out.data_ptr(), p["status"].data_ptr(), None, ops.stream_handle(value))
+        C.check(rc, "peer_allgather")
+        return out
+
+    def check(self):
+        """Synchronises and raises if an exchange kernel of this group gave up waiting for a rank."""
+        if self._peer is not None:
+            C.check(C.load().kf_check(self._peer["status"].data_ptr(), None), "sharded exchange")
+
+    def _peer_release(self):
+        if self._peer is None:
+            return
+        lib, p = C.load(), self._peer
+        with torch.cuda.device(p["device"]):
+            torch.cuda.synchronize()
+            for r, ptr in enumerate(p["ptrs"]):
+                if r != self.rank:
+                    lib.kf_ipc_close(ptr)
+            dist.barrier(group=self.group)
+            lib.kf_xbuf_free(p["mine"])
+        self._peer = None
 
     # ---- peer-memory exchange buffers (GPU ranks of one node) ---------------------------------------
     def exchange_buffers(self, nbytes, device):
@@ -103,6 +172,7 @@ class ShardGroup:
     def close(self):
         """Releases what the group holds on the device (collective)."""
         self.release_exchange_buffers()
+        self._peer_release()
         self._scratch = {}
 
     def scratch(self, name, numel, dtype, device):
@@ -191,6 +261,17 @@ def all_gather_vec(group: ShardGroup, x):
     return out
 
 
+def gather_one(group: ShardGroup, value, out=None):
+    """One element per rank (a shard total), in rank order, on every rank: through peer memory on GPUs of
+    one node, else through the communication library."""
+    if group.peer_memory and value.is_cuda and group.world <= 64 and value.numel() * value.element_size() <= 8:
+        return group.peer_allgather(value, out=out)
+    if out is None:
+        return all_gather_vec(group, value)
+    dist.all_gather_into_tensor(_wire_view(out)[0], _wire_view(value.contiguous())[0], group=group.group)
+    return out
+
+
 # ---- mapreduce -----------------------------------------------------------------------------------
 def mapreduce(group: ShardGroup, f, op, x, *, g=ops.identity, local: LocalOps = _DEFAULT_OPS, to_cpu=True):
     """Global g(op-reduce f(x)) over all shards; every rank gets the value."""
@@ -199,7 +280,12 @@ def mapreduce(group: ShardGroup, f, op, x, *, g=ops.identity, local: LocalOps = 
         raise C.ArgumentError("AffineCompose is not commutative: use scan")
     gcode = ops.post_code(g)
     part = local.reduce(f, op, x, out=group.scratch("partial", 1, x.dtype, x.device))
-    if opcode in _NCCL_REDUCE and part.dtype in _NCCL_DTYPES:
+    if group.peer_memory and part.is_cuda and group.world <= 64:
+        # partials of all ranks through peer memory, folded in rank order by one small kernel (with g):
+        # deterministic, any operator, no communication-library call
+        every = gather_one(group, part, out=group.scratch("partials", group.world, x.dtype, x.device))
+        total = local.fold(op, every, g=g)
+    elif opcode in _NCCL_REDUCE and part.dtype in _NCCL_DTYPES:
         dist.all_reduce(part, op=_NCCL_REDUCE[opcode], group=group.group)
         if gcode == C.POST_IDENTITY:
             total = part
@@ -236,38 +322,43 @@ def scan_(group: ShardGroup, *args, tmp=None, g=ops.identity, local: LocalOps = 
             total = torch.stack([dst[0][-1], dst[1][-1]])
         else:
             total = dst[-1].clone()
-        totals = all_gather_vec(group, total)  # (a, b) pairs in rank order
+        totals = gather_one(group, total)  # (a, b) pairs in rank order
         if group.rank == 0:
             return dst
         return local.scan_(f, op, dst, src, init=totals[: 2 * group.rank], tmp=tmp)
     total = local.reduce(f, op, src, out=group.scratch("partial", 1, src.dtype, src.device))
-    totals = all_gather_vec(group, total)
+    totals = gather_one(group, total, out=group.scratch("totals", group.world, src.dtype, src.device))
     # the scan kernel folds the totals of the shards before this one itself (ninit = rank)
     init = totals[: group.rank] if group.rank > 0 else None
     return local.scan_(f, op, dst, src, init=init, tmp=tmp, **kw)
 
 
 def scan_many_(group: ShardGroup, jobs, *, local: LocalOps = _DEFAULT_OPS):
-    """Several sharded scans whose exchanges hide behind the local kernels: `jobs` are (op, dst, src) or
-    (op, dst, src, tmp) tuples with elementwise operators (AffineCompose goes through `scan_`).
-    Order of work: reduce job 0, start its allgather (asynchronously, on the communication stream),
-    reduce job 1, start its allgather, ..., then for each job wait for its totals and run the seeded
-    scan. The allgather of job i runs while job i+1 is reduced (or job i-1 is scanned), so what a step
-    exposes of the exchange is close to nothing instead of one latency per array."""
+    """Several sharded scans in one go: `jobs` are (op, dst, src) or (op, dst, src, tmp) tuples with
+    elementwise operators (AffineCompose goes through `scan_`). Order of work: reduce job 0, exchange its
+    total, reduce job 1, exchange its total, ..., then the seeded scans. On GPUs of one node the exchange
+    is `kf_peer_allgather`, a kernel on the same stream (a few microseconds, no host involvement); with a
+    communication library it is an asynchronous allgather that runs behind the next job's reduction."""
     if group.world == 1:
         return [local.scan_(ops.identity, j[0], j[1], j[2], tmp=j[3] if len(j) > 3 else None) for j in jobs]
     if any(isinstance(j[0], ops.AffineCompose) for j in jobs):
         raise C.ArgumentError("scan_many_ takes elementwise operators; use scan_ for AffineCompose")
+    peer = group.peer_memory and jobs[0][2].is_cuda and group.world <= 64
     pending = []
     for i, j in enumerate(jobs):
         src = j[2]
         part = local.reduce(ops.identity, j[0], src, out=group.scratch("many_partial%d" % i, 1, src.dtype, src.device))
         totals = group.scratch("many_totals%d" % i, group.world, src.dtype, src.device)
-        work = dist.all_gather_into_tensor(_wire_view(totals)[0], _wire_view(part)[0], group=group.group, async_op=True)
-        pending.append((work, totals))
+        if peer:  # a kernel of the library on the same stream: nothing to wait for on the host side
+            group.peer_allgather(part, out=totals)
+            pending.append((None, totals))
+        else:
+            work = dist.all_gather_into_tensor(_wire_view(totals)[0], _wire_view(part)[0], group=group.group, async_op=True)
+            pending.append((work, totals))
     outs = []
     for (work, totals), j in zip(pending, jobs):
-        work.wait()
+        if work is not None:
+            work.wait()
         # the scan kernel folds the totals of the shards before this one itself (ninit = rank)
         init = totals[: group.rank] if group.rank > 0 else None
         outs.append(local.scan_(ops.identity, j[0], j[1], j[2], init=init, tmp=j[3] if len(j) > 3 else None))

@@ -427,6 +427,17 @@ ipc_close(p::CuPtr{Cvoid}) = check(ccall((:kf_ipc_close, libkf), Cint, (CuPtr{Cv
 copy_d2d(dst::CuPtr{Cvoid}, src::CuPtr{Cvoid}, nbytes::Integer) =
     check(ccall((:kf_copy_d2d, libkf), Cint, (CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, Ptr{Cvoid}), dst, src, nbytes, stream_handle()), "copy_d2d")
 
+peer_region_bytes() = ccall((:kf_peer_region_bytes, libkf), Csize_t, ())
+"One element per rank, gathered over peer memory by a kernel of the library (see include/kf_b200.h)."
+function peer_allgather!(out::CuArray{T}, value::CuArray{T}, peers::CuArray{CuPtr{Cvoid}}, region::CuPtr{Cvoid},
+                         world::Integer, rank::Integer, epoch::Integer, status::CuArray{UInt8}) where {T}
+    check(ccall((:kf_peer_allgather, libkf), Cint,
+                (CuPtr{Cvoid}, CuPtr{Cvoid}, Cint, Cint, UInt32, CuPtr{Cvoid}, Cint, CuPtr{Cvoid}, CuPtr{Cvoid}, Ptr{LaunchCfg}, Ptr{Cvoid}),
+                pointer(peers), region, world, rank, epoch, pointer(value), sizeof(T), pointer(out), pointer(status),
+                cfg_ptr(nothing), stream_handle()), "peer_allgather!")
+    out
+end
+
 # ---- library -------------------------------------------------------------------------------------------
 launch_count() = ccall((:kf_launch_count, libkf), UInt64, ())
 num_sms() = Int(ccall((:kf_num_sms, libkf), Cint, ()))
