@@ -368,8 +368,12 @@ def run_case(args):
         da, db = torch.empty_like(a), torch.empty_like(b)
         tmp = kf.get_allocation(kf.Scan1D, kf.identity, kf.AffineCompose(), (a, b))
         fn, nbytes = (lambda: kf.scan_(kf.AffineCompose(), (da, db), (a, b), tmp=tmp)), 16 * n
-    elif case in ("sort_u32", "sort_f32", "sort_pairs", "sort_u64"):
-        if case == "sort_f32":
+    elif case in ("sort_u32", "sort_f32", "sort_pairs", "sort_u64", "sort_u8", "sort_i16"):
+        if case == "sort_u8":
+            keys = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=g)
+        elif case == "sort_i16":
+            keys = torch.randint(-32768, 32768, (n,), dtype=torch.int16, device="cuda", generator=g)
+        elif case == "sort_f32":
             keys = torch.randn(n, dtype=torch.float32, device="cuda", generator=g)
         elif case == "sort_u64":
             keys = torch.randint(-2**63, 2**63 - 1, (n,), dtype=torch.int64, device="cuda", generator=g).view(torch.uint64)
@@ -383,7 +387,7 @@ def run_case(args):
             fn, nbytes = (lambda: kf.sort_(vout, idx, keys=keys, keys_dst=out, tmp=tmp)), 68 * n
         else:
             tmp = kf.get_allocation(kf.Sort1D, keys)
-            fn, nbytes = (lambda: kf.sort_(out, keys, tmp=tmp)), (136 if case == "sort_u64" else 36) * n
+            fn, nbytes = (lambda: kf.sort_(out, keys, tmp=tmp)), {"sort_u64": 136, "sort_u8": 3, "sort_i16": 10}.get(case, 36) * n
     else:
         raise SystemExit("unknown --case %r" % case)
     fn()
@@ -849,7 +853,7 @@ def main():
     ap.add_argument("--detail", type=int, default=1, help="1: also measure the other primitives (single GPU)")
     ap.add_argument("--case", default=None,
                     help="run ONE primitive a few times at n=2^log2n and exit (small case for profiler captures): "
-                         "scan_u32, scan_f32, scan_f64, scan_u8, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_u64, sort_pairs")
+                         "scan_u32, scan_f32, scan_f64, scan_u8, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_u64, sort_u8, sort_i16, sort_pairs")
     ap.add_argument("--log2n", type=int, default=26)
     ap.add_argument("--n", type=int, default=0, help="with --case: an exact element count instead of 2^log2n")
     ap.add_argument("--sharded", action="store_true",

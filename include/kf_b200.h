@@ -251,9 +251,11 @@ size_t kf_sort_workspace_bytes(int32_t key_dtype, int32_t val_bytes, uint64_t n,
  * Replaces _sort1d_impl! (src/sort/sort1d.jl:780-874), _sort_histograms! (:655-697),
  * bucket_histogram_kernel! (src/sort/bucket_histogram_kernel.jl:77-145),
  * scan_histogram_kernel! (src/sort/scan_histogram_kernel.jl:20-46) and the onesweep pass
- * kernel (src/sort/onesweep_kernel.jl:113-488); one-byte keys take the same kernel with a single
- * pass instead of the reference's byte_sort_kernel (src/sort/byte_sort_kernel.jl:32-167), which is
- * not stable across blocks. n == 0 is a no-op. */
+ * kernel (src/sort/onesweep_kernel.jl:113-488). One-byte keys replace the reference's
+ * byte_sort_kernel (src/sort/byte_sort_kernel.jl:32-167): without a payload equal keys are the
+ * same byte, so kf_sort_keys writes the 256 runs of the histogram out instead of scattering keys
+ * (two-byte keys the same way with 65 536 bins from 2^22 keys on); with a payload (kf_sort_pairs)
+ * they take the stable onesweep kernel with a single pass. n == 0 is a no-op. */
 int32_t kf_sort_keys(int32_t key_dtype, const void *src, void *dst, uint64_t n,
                      void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 

@@ -22,6 +22,200 @@ __global__ void sort_scan_histogram_kernel(u64 *ghist) {
     h[tid] = base + incl - c;
 }
 
+// One-byte keys without a payload: equal keys are the same byte, so the sorted array is the histogram
+// written out as 256 runs. gexcl[d] is the start of digit d's run (digit = byte ^ top_xor, the sign flip
+// of signed keys). Each CTA fills one contiguous piece of dst with 128-bit stores; a thread's positions
+// only grow, so it walks the run boundaries forward from one binary search at the start of the piece.
+// The 1-byte path of the reference (src/sort/byte_sort_kernel.jl:1-17) still scatters every key.
+__global__ void __launch_bounds__(256) byte_runs_fill_kernel(uint8_t *dst, u64 n, const u64 *gexcl, u32 top_xor) {
+    __shared__ u64 s_excl[kRadix + 1];
+    const u32 tid = threadIdx.x;
+    s_excl[tid] = gexcl[tid];
+    if (tid == 0) s_excl[kRadix] = n;
+    __syncthreads();
+    auto digit_at = [&](u64 j) {  // the digit whose run holds position j < n (the largest d with start <= j)
+        int lo = 0, hi = kRadix;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_excl[mid] <= j) lo = mid;
+            else hi = mid;
+        }
+        return lo;
+    };
+    u64 head = (16 - ((uintptr_t)dst & 15u)) & 15u;  // bytes before the first 16-byte boundary
+    if (head > n) head = n;
+    const u64 nvec = (n - head) / 16;
+    const u64 per_cta = (nvec + gridDim.x - 1) / gridDim.x;
+    const u64 v_lo = (u64)blockIdx.x * per_cta;
+    const u64 v_hi = v_lo + per_cta < nvec ? v_lo + per_cta : nvec;
+    if (v_lo + tid < v_hi) {
+        int d = digit_at(head + (v_lo + tid) * 16);
+        for (u64 v = v_lo + tid; v < v_hi; v += 256) {
+            const u64 j0 = head + v * 16;
+            while (s_excl[d + 1] <= j0) ++d;
+            uint4 o;
+            if (s_excl[d + 1] >= j0 + 16) {  // the whole vector lies in one run
+                const u32 w = ((u32)d ^ top_xor) * 0x01010101u;
+                o = make_uint4(w, w, w, w);
+            } else {
+                uint8_t b[16];
+                int e_d = d;
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    while (s_excl[e_d + 1] <= j0 + e) ++e_d;
+                    b[e] = (uint8_t)((u32)e_d ^ top_xor);
+                }
+                memcpy(&o, b, 16);
+            }
+            st_stream_v4(dst + j0, o);
+        }
+    }
+    if (blockIdx.x == 0) {  // the ragged ends
+        const u64 tail = head + nvec * 16;
+        if (tid < head) dst[tid] = (uint8_t)((u32)digit_at(tid) ^ top_xor);
+        if (tid < 16 && tail + tid < n) dst[tail + tid] = (uint8_t)((u32)digit_at(tail + tid) ^ top_xor);
+    }
+}
+
+// Two-byte keys without a payload, large n: the same idea with 65 536 bins. A CTA cannot hold that
+// many 32-bit counters, so the CTAs work in pairs over the same piece of the input: the even CTA counts
+// the keys whose mapped value is below 32 768, the odd one the rest (128 KB of counters each; the
+// second read of a piece comes from L2). `flip` is 0x8000 for signed keys (the uint_map sign flip).
+constexpr int kShortBins = 65536;
+constexpr u64 kShortRunsMinN = 1ull << 22;  // below this the two-pass onesweep is used (and the counters would not fit the scratch)
+__global__ void __launch_bounds__(1024) short_histogram_kernel(const uint16_t *__restrict__ keys, u64 n, u64 *gcount, u32 flip) {
+    extern __shared__ __align__(16) u32 sh_half[];  // [32768]
+    const u32 tid = threadIdx.x, role = blockIdx.x & 1u;
+    const u64 pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    for (u32 i = tid; i < kShortBins / 2 / 4; i += 1024) reinterpret_cast<uint4 *>(sh_half)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    auto count_key = [&](u32 k) {
+        const u32 m = k ^ flip;
+        if ((m >> 15) == role) atomicAdd(&sh_half[m & 0x7FFFu], 1u);
+    };
+    const u64 mis = ((uintptr_t)keys & 15u) / 2;
+    u64 head = mis ? 8 - mis : 0;
+    if (head > n) head = n;
+    const u64 nvec = (n - head) / 8;
+    const uint4 *vsrc = reinterpret_cast<const uint4 *>(keys + head);
+    constexpr int UNROLL = 4;
+    const u64 strip = 1024ull * UNROLL;
+    for (u64 base = pair * strip; base < nvec; base += npairs * strip) {
+        uint4 v[UNROLL];
+        bool ok[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const u64 idx = base + (u64)u * 1024 + tid;
+            ok[u] = idx < nvec;
+            if (ok[u]) v[u] = ld_stream_v4(vsrc + idx);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (ok[u]) {
+                const u32 w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    count_key(w[q] & 0xFFFFu);
+                    count_key(w[q] >> 16);
+                }
+            }
+        }
+    }
+    if (pair == 0) {  // the ragged ends (fewer than 8 keys each)
+        const u64 tail = head + nvec * 8;
+        if (tid < head) count_key(keys[tid]);
+        if (tid < 8 && tail + tid < n) count_key(keys[tail + tid]);
+    }
+    __syncthreads();
+    for (u32 i = tid; i < kShortBins / 2; i += 1024) {
+        const u32 c = sh_half[i];
+        if (c) atomicAdd(reinterpret_cast<unsigned long long *>(gcount) + role * (kShortBins / 2) + i, (unsigned long long)c);
+    }
+}
+
+// Exclusive prefix of the 65 536 counts in place, and the total in entry 65 536. One CTA of 32 warps;
+// a warp owns 2048 consecutive bins and reads them 32 at a time (coalesced), twice: once for its
+// total, once for the running prefix.
+__global__ void __launch_bounds__(1024) short_scan_kernel(u64 *gcount) {
+    __shared__ u64 s_warp[32];
+    const u32 tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    u64 *seg = gcount + (size_t)warp * (kShortBins / 32);
+    u64 part = 0;
+    for (int it = 0; it < kShortBins / 1024; ++it) part += seg[it * 32 + lane];
+#pragma unroll
+    for (int d = 16; d; d >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, d);
+    if (lane == 0) s_warp[warp] = part;
+    __syncthreads();
+    u64 run = 0;
+    for (u32 w = 0; w < warp; ++w) run += s_warp[w];
+    for (int it = 0; it < kShortBins / 1024; ++it) {
+        const u64 c = seg[it * 32 + lane];
+        u64 incl = c;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const u64 up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= (u32)d) incl += up;
+        }
+        seg[it * 32 + lane] = run + incl - c;
+        run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+    }
+    if (tid == 1023) gcount[kShortBins] = run;
+}
+
+// dst = the 65 536 runs. excl[d] is the start of the run of mapped value d, excl[65536] = n. A thread's
+// positions only grow, so it walks the run boundaries forward; after 24 steps without reaching its
+// position (sparse keys: long stretches of empty bins) it falls back to a binary search.
+__global__ void __launch_bounds__(256) short_runs_fill_kernel(uint16_t *dst, u64 n, const u64 *__restrict__ excl, u32 flip) {
+    const u32 tid = threadIdx.x;
+    auto digit_at = [&](u64 j) {  // the largest d with excl[d] <= j, for j < n
+        int lo = 0, hi = kShortBins;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (__ldg(excl + mid) <= j) lo = mid;
+            else hi = mid;
+        }
+        return lo;
+    };
+    auto advance = [&](int d, u64 j) {  // from a digit at or before j's to j's
+        for (int steps = 0; __ldg(excl + d + 1) <= j; ++d)
+            if (++steps == 24) return digit_at(j);
+        return d;
+    };
+    u64 head = ((16 - ((uintptr_t)dst & 15u)) & 15u) / 2;  // elements before the first 16-byte boundary
+    if (head > n) head = n;
+    const u64 nvec = (n - head) / 8;
+    const u64 per_cta = (nvec + gridDim.x - 1) / gridDim.x;
+    const u64 v_lo = (u64)blockIdx.x * per_cta;
+    const u64 v_hi = v_lo + per_cta < nvec ? v_lo + per_cta : nvec;
+    if (v_lo + tid < v_hi) {
+        int d = digit_at(head + (v_lo + tid) * 8);
+        for (u64 v = v_lo + tid; v < v_hi; v += 256) {
+            const u64 j0 = head + v * 8;
+            d = advance(d, j0);
+            uint4 o;
+            if (__ldg(excl + d + 1) >= j0 + 8) {  // the whole vector lies in one run
+                const u32 w = ((u32)d ^ flip) * 0x00010001u;
+                o = make_uint4(w, w, w, w);
+            } else {
+                uint16_t b[8];
+                int e_d = d;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    e_d = advance(e_d, j0 + e);
+                    b[e] = (uint16_t)((u32)e_d ^ flip);
+                }
+                memcpy(&o, b, 16);
+            }
+            st_stream_v4(dst + j0, o);
+        }
+    }
+    if (blockIdx.x == 0) {  // the ragged ends
+        const u64 tail = head + nvec * 8;
+        if (tid < head) dst[tid] = (uint16_t)((u32)digit_at(tid) ^ flip);
+        if (tid < 8 && tail + tid < n) dst[tail + tid] = (uint16_t)((u32)digit_at(tail + tid) ^ flip);
+    }
+}
+
 struct KeyInfo {
     int bytes;
     bool is_float;
@@ -98,7 +292,31 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
     void *kscratch = base + p.off_keys;
     void *vscratch = base + p.off_vals;
 
-    KF_CUDA_TRY(cudaMemsetAsync(ws, 0, p.clear_bytes, s));
+    // One-byte keys alone (no payload; not under the bounded-wait test hook, which needs the look-back):
+    // histogram, 256-bin scan, runs written out. In place works as it is: the histogram has read src
+    // before the fill starts.
+    const bool byte_runs = k.bytes == 1 && val_bytes == 0 && test_mute_tile(cfg) == 0;
+    // Two-byte keys alone, from kShortRunsMinN keys: 65 536-bin histogram (counters in the key scratch,
+    // which this path does not otherwise need), scan, runs written out.
+    if (k.bytes == 2 && val_bytes == 0 && n >= kShortRunsMinN && test_mute_tile(cfg) == 0) {
+        u64 *gcount = (u64 *)kscratch;
+        const u32 flip = k.signed_or_float ? 0x8000u : 0u;
+        KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes, s));
+        KF_CUDA_TRY(cudaMemsetAsync(gcount, 0, (size_t)(kShortBins + 1) * 8, s));
+        const int pairs = device_sm_count() / 2 > 0 ? device_sm_count() / 2 : 1;
+        constexpr size_t kSmem = (size_t)kShortBins / 2 * 4;
+        KF_CUDA_TRY(cudaFuncSetAttribute(short_histogram_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
+        short_histogram_kernel<<<2 * pairs, 1024, kSmem, s>>>((const uint16_t *)keys_src, n, gcount, flip); note_launch();
+        short_scan_kernel<<<1, 1024, 0, s>>>(gcount); note_launch();
+        const u64 nvec = n / 8;
+        u64 blocks = (nvec + 255) / 256;
+        const u64 cap = (u64)device_sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+        short_runs_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>((uint16_t *)keys_dst, n, gcount, flip); note_launch();
+        KF_CUDA_TRY(cudaGetLastError());
+        return KF_OK;
+    }
+    KF_CUDA_TRY(cudaMemsetAsync(ws, 0, byte_runs ? p.off_desc : p.clear_bytes, s));
     switch (k.bytes) {
     case 1: rc = sort_hist_k8(keys_src, n, ghist, k.signed_or_float, s); break;
     case 2: rc = sort_hist_k16(keys_src, n, ghist, k.signed_or_float, s); break;
@@ -108,6 +326,16 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
     if (rc != KF_OK) return rc;
     sort_scan_histogram_kernel<<<k.bytes, kRadix, 0, s>>>(ghist); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
+    if (byte_runs) {
+        const u64 nvec = n / 16;
+        u64 blocks = (nvec + 255) / 256;
+        const u64 cap = (u64)device_sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        byte_runs_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>((uint8_t *)keys_dst, n, ghist, k.signed_or_float ? 0x80u : 0u); note_launch();
+        KF_CUDA_TRY(cudaGetLastError());
+        return KF_OK;
+    }
 
     // Ping-pong plan: pass p writes dst when the number of passes still to come is even, else the
     // scratch; pass 0 reads src. With an even pass count this never writes src unless dst == src,

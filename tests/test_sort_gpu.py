@@ -42,6 +42,73 @@ def test_keys_types_sizes(kf, oracle, dtype, n):
     assert_same_bits(to_host(src), oracle.c_sort(x))
 
 
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8])
+def test_one_byte_keys_runs_path(kf, oracle, dtype):
+    """One-byte keys without payload are written out as the 256 runs of their histogram: every size
+    around the 16-byte vector width, every alignment of dst and src, sparse and one-valued inputs,
+    in place, and the single-pass onesweep kernel (taken with a payload) as a second opinion."""
+    rng = np.random.default_rng(77)
+    info = np.iinfo(dtype)
+    for n in (1, 2, 15, 16, 17, 31, 32, 33, 255, 256, 1000, 4097, 65_537, 1_000_003, 9_000_001):
+        cases = [rng.integers(info.min, info.max, n, dtype=dtype, endpoint=True),
+                 np.full(n, info.min, dtype=dtype), np.full(n, info.max, dtype=dtype),
+                 rng.choice(np.array([info.min, -1 if info.min < 0 else 127, 0, 5, info.max], dtype=dtype), n),
+                 (np.arange(n) % 256).astype(np.uint8).view(dtype)]
+        for x in cases:
+            assert_same_bits(to_host(kf.sort(to_dev(x))), oracle.c_sort(x))
+    x = rng.integers(info.min, info.max, 100_000, dtype=dtype, endpoint=True)
+    for off_src in (0, 1, 7):
+        for off_dst in (0, 1, 3, 8, 15):
+            for n in (5, 40, 99_000):
+                big_src = to_dev(x)
+                big_dst = torch.zeros(100_000 + 64, dtype=big_src.dtype, device="cuda")
+                kf.sort_(big_dst[off_dst:off_dst + n], big_src[off_src:off_src + n])
+                got = to_host(big_dst)
+                assert_same_bits(got[off_dst:off_dst + n], oracle.c_sort(x[off_src:off_src + n]))
+                assert not got[:off_dst].any() and not got[off_dst + n:].any()  # nothing outside dst
+    src = to_dev(x)
+    kf.sort_(src[3:90_003])  # in place on a misaligned view
+    got = to_host(src)
+    assert_same_bits(got[3:90_003], oracle.c_sort(x[3:90_003]))
+    assert_same_bits(got[:3], x[:3])
+    assert_same_bits(got[90_003:], x[90_003:])
+    vals = torch.arange(100_000, dtype=torch.int32, device="cuda")
+    _, keys_sorted = kf.sort(vals, keys=to_dev(x))
+    assert_same_bits(to_host(keys_sorted), to_host(kf.sort(to_dev(x))))
+
+
+@pytest.mark.parametrize("dtype", [np.uint16, np.int16])
+def test_two_byte_keys_runs_path(kf, oracle, dtype):
+    """Two-byte keys without payload, from 2^22 keys on, are written out as the 65 536 runs of their
+    histogram: dense and sparse value sets (long stretches of empty bins), one value, every value
+    once among long runs, misaligned and in-place arrays; the size just below takes the onesweep."""
+    rng = np.random.default_rng(78)
+    info = np.iinfo(dtype)
+    every = np.arange(65536, dtype=np.uint16).view(dtype)
+    for n in ((1 << 22) - 1, 1 << 22, (1 << 22) + 13, 6_000_001):
+        cases = [rng.integers(info.min, info.max, n, dtype=dtype, endpoint=True),
+                 np.full(n, info.min, dtype=dtype),
+                 rng.choice(np.array([info.min, info.min + 1, 0, 77, 30_000, info.max], dtype=dtype), n),
+                 rng.integers(0, 1000, n).astype(dtype),
+                 np.concatenate([every, np.full(n - 65536, 12_345, dtype=dtype)])[rng.permutation(n)]]
+        for x in cases:
+            assert_same_bits(to_host(kf.sort(to_dev(x))), oracle.c_sort(x))
+    n = (1 << 22) + 40
+    x = rng.integers(info.min, info.max, n + 16, dtype=dtype, endpoint=True)
+    for off_src, off_dst in ((0, 1), (1, 0), (3, 7), (5, 5)):
+        big_dst = torch.zeros(n + 32, dtype=to_dev(x[:1]).dtype, device="cuda")
+        kf.sort_(big_dst[off_dst:off_dst + n], to_dev(x)[off_src:off_src + n])
+        got = to_host(big_dst)
+        assert_same_bits(got[off_dst:off_dst + n], oracle.c_sort(x[off_src:off_src + n]))
+        assert not got[:off_dst].any() and not got[off_dst + n:].any()  # nothing outside dst
+    src = to_dev(x)
+    kf.sort_(src[3:3 + n])  # in place on a misaligned view
+    got = to_host(src)
+    assert_same_bits(got[3:3 + n], oracle.c_sort(x[3:3 + n]))
+    assert_same_bits(got[:3], x[:3])
+    assert_same_bits(got[3 + n:], x[3 + n:])
+
+
 @pytest.mark.parametrize("n", list(range(1, 17)))
 def test_tiny_sizes(kf, oracle, n):
     for dtype in (np.uint32, np.float32):
