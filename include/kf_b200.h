@@ -197,6 +197,20 @@ int32_t kf_scan_affine_soa(const float *a_src, const float *b_src, float *a_dst,
 int32_t kf_scan_affine_aos(const float *ab_src, float *ab_dst, uint64_t n, const float *init_ab, uint32_t ninit,
                            void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
 
+/* Workspace for kf_scan_quaternion (dtype KF_F32 or KF_F64 = the component type; 0 otherwise).
+ * In reference terms get_allocation(Scan1D, ...) for a Quaternion element type
+ * (src/scan/scan.jl:156-211, split layout). */
+size_t kf_scan_quaternion_workspace_bytes(int32_t dtype, uint64_t n);
+
+/* Inclusive scan of quaternions under the Hamilton product, which is not commutative:
+ * dst[i] = src[0] * src[1] * ... * src[i]. An element is four consecutive components (w, x, y, z) of
+ * type `dtype` (KF_F32: 16 bytes, KF_F64: 32 bytes), the layout of Quaternions.jl's Quaternion{T}.
+ * `init` points to `ninit` quaternions that seed the scan from the left, or is NULL. This is the
+ * reference's own non-commutative scan case, scan!(*, dst, src) over QuaternionF64 on the split
+ * kernel (test/tests/scan/scan_test.jl:22-33, src/scan/scan_kernel.jl:94-299). */
+int32_t kf_scan_quaternion(int32_t dtype, const void *src, void *dst, uint64_t n, const void *init, uint32_t ninit,
+                           void *ws, size_t ws_bytes, const kf_launch_cfg *cfg, kf_stream_t stream);
+
 /* Size of the fixed device array behind kf_scan_static: 1 MiB, held by every GPU that loads the
  * library until the process exits. It bounds the input: the call is refused when
  * kf_scan_workspace_bytes(dtype, 0, n, NULL) exceeds it. Largest n accepted, by element width

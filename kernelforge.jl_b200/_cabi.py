@@ -68,6 +68,9 @@ PROTOTYPES = {
                                      c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_scan_affine_aos": (c_int32, [c_void_p, c_void_p, c_uint64, c_void_p, c_uint32,
                                      c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
+    "kf_scan_quaternion_workspace_bytes": (c_size_t, [c_int32, c_uint64]),
+    "kf_scan_quaternion": (c_int32, [c_int32, c_void_p, c_void_p, c_uint64, c_void_p, c_uint32,
+                                     c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),
     "kf_sort_workspace_bytes": (c_size_t, [c_int32, c_int32, c_uint64, POINTER(LaunchCfg)]),
     "kf_sort_keys": (c_int32, [c_int32, c_void_p, c_void_p, c_uint64,
                                c_void_p, c_size_t, POINTER(LaunchCfg), c_void_p]),

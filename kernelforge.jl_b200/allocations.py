@@ -64,6 +64,10 @@ def scan_bytes(dtype_code: int, pair: bool, n: int, cfg) -> int:
     return C.load().kf_scan_workspace_bytes(dtype_code, 1 if pair else 0, n, cfg)
 
 
+def quaternion_scan_bytes(dtype_code: int, n: int) -> int:
+    return C.load().kf_scan_quaternion_workspace_bytes(dtype_code, n)
+
+
 def sort_bytes(key_code: int, val_bytes: int, n: int, cfg) -> int:
     return C.load().kf_sort_workspace_bytes(key_code, val_bytes, n, cfg)
 
@@ -93,6 +97,8 @@ def get_allocation(tag, *args, **kwargs) -> KernelBuffer:
             n = a.shape[0]
             return _alloc(tag, scan_bytes(C.F32, True, n, cfg), a.device)
         ops.require_device_vector(src, "src")
+        if isinstance(op, ops.QuaternionMul):
+            return _alloc(tag, quaternion_scan_bytes(ops.dtype_code(src), src.shape[0]), src.device)
         return _alloc(tag, scan_bytes(ops.dtype_code(src), False, src.numel(), cfg), src.device)
     if tag is Sort1D:
         src = args[0]

@@ -192,6 +192,32 @@ struct OpAffine {
     }
 };
 
+// Quaternion w + xi + yj + zk stored as four consecutive scalars (the layout of Quaternions.jl's
+// Quaternion{T}: s, v1, v2, v3) and the Hamilton product, the non-commutative operator that the
+// reference's scan test uses (test/tests/scan/scan_test.jl:22-33 of KernelForge.jl).
+template <typename F> struct Quat {
+    F w, x, y, z;
+};
+struct OpQuatMul {
+    static constexpr bool commutative = false;
+    template <typename T> static __device__ __forceinline__ T apply(T l, T r) {
+        T o;
+        o.w = l.w * r.w - l.x * r.x - l.y * r.y - l.z * r.z;
+        o.x = l.w * r.x + l.x * r.w + l.y * r.z - l.z * r.y;
+        o.y = l.w * r.y - l.x * r.z + l.y * r.w + l.z * r.x;
+        o.z = l.w * r.z + l.x * r.y - l.y * r.x + l.z * r.w;
+        return o;
+    }
+    template <typename T> static __device__ __forceinline__ T identity() {
+        T o;
+        o.w = 1;
+        o.x = 0;
+        o.y = 0;
+        o.z = 0;
+        return o;
+    }
+};
+
 // Element-wise map f, selected at run time (uniform across the grid; the kernels are
 // HBM-bound, the branch is free).
 template <typename T> __device__ __forceinline__ T apply_map(int f, T x) {
@@ -220,76 +246,40 @@ template <typename T> __device__ __forceinline__ T apply_post(int g, T x) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Warp shuffles for any 4- or 8-byte trivially copyable type.
+// Warp shuffles for any trivially copyable type of up to 4 bytes or of a multiple of 4 bytes
+// (8-byte scalars, the affine pair, quaternions): one 32-bit shuffle per word.
 // ---------------------------------------------------------------------------------------------
-template <typename T> __device__ __forceinline__ T shfl_up(T v, int d) {
-    if constexpr (sizeof(T) == 8) {
-        u64 x;
-        memcpy(&x, &v, 8);
-        x = __shfl_up_sync(0xFFFFFFFFu, x, d);
-        T o;
-        memcpy(&o, &x, 8);
-        return o;
-    } else {
-        static_assert(sizeof(T) <= 4, "unsupported shuffle width");
+template <typename T, typename Shuffle> __device__ __forceinline__ T shfl_words(T v, Shuffle sh) {
+    if constexpr (sizeof(T) <= 4) {
         u32 x = 0;
         memcpy(&x, &v, sizeof(T));
-        x = __shfl_up_sync(0xFFFFFFFFu, x, d);
+        x = sh(x);
         T o;
         memcpy(&o, &x, sizeof(T));
         return o;
+    } else {
+        static_assert(sizeof(T) % 4 == 0, "unsupported shuffle width");
+        constexpr int W = sizeof(T) / 4;
+        u32 x[W];
+        memcpy(x, &v, sizeof(T));
+#pragma unroll
+        for (int i = 0; i < W; ++i) x[i] = sh(x[i]);
+        T o;
+        memcpy(&o, x, sizeof(T));
+        return o;
     }
+}
+template <typename T> __device__ __forceinline__ T shfl_up(T v, int d) {
+    return shfl_words(v, [d](u32 x) { return __shfl_up_sync(0xFFFFFFFFu, x, d); });
 }
 template <typename T> __device__ __forceinline__ T shfl_down(T v, int d) {
-    if constexpr (sizeof(T) == 8) {
-        u64 x;
-        memcpy(&x, &v, 8);
-        x = __shfl_down_sync(0xFFFFFFFFu, x, d);
-        T o;
-        memcpy(&o, &x, 8);
-        return o;
-    } else {
-        u32 x = 0;
-        memcpy(&x, &v, sizeof(T));
-        x = __shfl_down_sync(0xFFFFFFFFu, x, d);
-        T o;
-        memcpy(&o, &x, sizeof(T));
-        return o;
-    }
+    return shfl_words(v, [d](u32 x) { return __shfl_down_sync(0xFFFFFFFFu, x, d); });
 }
 template <typename T> __device__ __forceinline__ T shfl_xor(T v, int m) {
-    if constexpr (sizeof(T) == 8) {
-        u64 x;
-        memcpy(&x, &v, 8);
-        x = __shfl_xor_sync(0xFFFFFFFFu, x, m);
-        T o;
-        memcpy(&o, &x, 8);
-        return o;
-    } else {
-        u32 x = 0;
-        memcpy(&x, &v, sizeof(T));
-        x = __shfl_xor_sync(0xFFFFFFFFu, x, m);
-        T o;
-        memcpy(&o, &x, sizeof(T));
-        return o;
-    }
+    return shfl_words(v, [m](u32 x) { return __shfl_xor_sync(0xFFFFFFFFu, x, m); });
 }
 template <typename T> __device__ __forceinline__ T shfl_idx(T v, int src) {
-    if constexpr (sizeof(T) == 8) {
-        u64 x;
-        memcpy(&x, &v, 8);
-        x = __shfl_sync(0xFFFFFFFFu, x, src);
-        T o;
-        memcpy(&o, &x, 8);
-        return o;
-    } else {
-        u32 x = 0;
-        memcpy(&x, &v, sizeof(T));
-        x = __shfl_sync(0xFFFFFFFFu, x, src);
-        T o;
-        memcpy(&o, &x, sizeof(T));
-        return o;
-    }
+    return shfl_words(v, [src](u32 x) { return __shfl_sync(0xFFFFFFFFu, x, src); });
 }
 
 // Inclusive warp scan that keeps operand order (lane i holds x_0 op ... op x_i).

@@ -12,9 +12,9 @@
 // Tiles are handed out by an atomic ticket, so a tile's predecessors are always already running.
 // Each tile publishes its aggregate, looks back over its predecessors' descriptors with one warp
 // (32 descriptors per poll), then publishes its inclusive prefix. A descriptor is one 64-bit word
-// {status:32 | value:32} for elements up to 4 bytes, or two such words {status | low half},
-// {status | high half} for 8-byte elements: each word validates itself and a reader retries
-// until both carry the same status, so no fence separates value and flag. Every wait is
+// {status:32 | value:32} for elements up to 4 bytes, or one such word per 32 bits of a wider element
+// (two for 8-byte elements, eight for a Float64 quaternion): each word validates itself and a reader
+// retries until all carry the same status, so no fence separates value and flag. Every wait is
 // bounded; a tile that gives up records KF_ERR_TIMEOUT in the workspace header and publishes a
 // poison status that makes its successors return too.
 //
@@ -32,7 +32,7 @@ enum : u32 { kInvalid = 0, kAggregate = 1, kPrefix = 2, kPoison = 3 };
 
 // ---- descriptors ------------------------------------------------------------------------------
 template <typename T> struct Desc {
-    static constexpr int WORDS = sizeof(T) <= 4 ? 1 : 2;
+    static constexpr int WORDS = sizeof(T) <= 4 ? 1 : (int)(sizeof(T) / 4);
 
     static __device__ __forceinline__ void publish(u64 *desc, u64 tile, u32 status, T v) {
         if constexpr (WORDS == 1) {
@@ -40,13 +40,13 @@ template <typename T> struct Desc {
             memcpy(&bits, &v, sizeof(T));
             st_relaxed_u64(desc + tile, ((u64)status << 32) | bits);
         } else {
-            u32 h[2];
-            memcpy(h, &v, 8);
-            st_relaxed_u64(desc + 2 * tile, ((u64)status << 32) | h[0]);
-            st_relaxed_u64(desc + 2 * tile + 1, ((u64)status << 32) | h[1]);
+            u32 h[WORDS];
+            memcpy(h, &v, sizeof(T));
+#pragma unroll
+            for (int i = 0; i < WORDS; ++i) st_relaxed_u64(desc + WORDS * tile + i, ((u64)status << 32) | h[i]);
         }
     }
-    // Returns the status (kInvalid when not yet published or when the two halves disagree).
+    // Returns the status (kInvalid when not yet published or when the words disagree).
     static __device__ __forceinline__ u32 read(const u64 *desc, u64 tile, T &v) {
         if constexpr (WORDS == 1) {
             const u64 w = ld_relaxed_u64(desc + tile);
@@ -54,12 +54,19 @@ template <typename T> struct Desc {
             memcpy(&v, &bits, sizeof(T));
             return (u32)(w >> 32);
         } else {
-            const u64 w0 = ld_relaxed_u64(desc + 2 * tile);
-            const u64 w1 = ld_relaxed_u64(desc + 2 * tile + 1);
-            u32 h[2] = {(u32)w0, (u32)w1};
-            memcpy(&v, h, 8);
-            const u32 s0 = (u32)(w0 >> 32), s1 = (u32)(w1 >> 32);
-            return s0 == s1 ? s0 : (u32)kInvalid;
+            u32 h[WORDS];
+            u32 st = 0;
+            bool same = true;
+#pragma unroll
+            for (int i = 0; i < WORDS; ++i) {
+                const u64 w = ld_relaxed_u64(desc + WORDS * tile + i);
+                h[i] = (u32)w;
+                const u32 si = (u32)(w >> 32);
+                if (i == 0) st = si;
+                else same = same && si == st;
+            }
+            memcpy(&v, h, sizeof(T));
+            return same ? st : (u32)kInvalid;
         }
     }
 };
@@ -124,8 +131,47 @@ struct AffineSoaAccess {
     }
 };
 
+// Quaternions as an array of structs: a slot is one quaternion (one 16-byte vector for Float32
+// components, two for Float64).
+template <typename F> struct QuatAccess {
+    static constexpr int EPV = 1;
+    using Q = Quat<F>;
+    const Q *src;
+    Q *dst;
+    __device__ __forceinline__ void load_slot(u64 i, Q (&e)[1]) const {
+        uint4 v[sizeof(Q) / 16];
+#pragma unroll
+        for (int k = 0; k < (int)(sizeof(Q) / 16); ++k) v[k] = ld_v4(reinterpret_cast<const uint4 *>(src + i) + k);
+        memcpy(&e[0], v, sizeof(Q));
+    }
+    __device__ __forceinline__ void store_slot(u64 i, const Q (&e)[1]) const {
+        uint4 v[sizeof(Q) / 16];
+        memcpy(v, &e[0], sizeof(Q));
+#pragma unroll
+        for (int k = 0; k < (int)(sizeof(Q) / 16); ++k) st_stream_v4(reinterpret_cast<uint4 *>(dst + i) + k, v[k]);
+    }
+    __device__ __forceinline__ Q load_elem(u64 i) const {
+        const F *p = reinterpret_cast<const F *>(src + i);
+        Q q;
+        q.w = p[0];
+        q.x = p[1];
+        q.y = p[2];
+        q.z = p[3];
+        return q;
+    }
+    __device__ __forceinline__ void store_elem(u64 i, Q q) const {
+        F *p = reinterpret_cast<F *>(dst + i);
+        p[0] = q.w;
+        p[1] = q.x;
+        p[2] = q.y;
+        p[3] = q.z;
+    }
+};
+
 template <typename T> __device__ __forceinline__ T map_elem(int f, T x) { return apply_map<T>(f, x); }
 template <> __device__ __forceinline__ Affine map_elem<Affine>(int, Affine x) { return x; }
+template <> __device__ __forceinline__ Quat<float> map_elem<Quat<float>>(int, Quat<float> x) { return x; }
+template <> __device__ __forceinline__ Quat<double> map_elem<Quat<double>>(int, Quat<double> x) { return x; }
 
 struct ScanArgs {
     u64 n;          // elements
@@ -144,6 +190,8 @@ struct ScanArgs {
 
 template <typename T> __device__ __forceinline__ T post_elem(int g, T x) { return apply_post<T>(g, x); }
 template <> __device__ __forceinline__ Affine post_elem<Affine>(int, Affine x) { return x; }
+template <> __device__ __forceinline__ Quat<float> post_elem<Quat<float>>(int, Quat<float> x) { return x; }
+template <> __device__ __forceinline__ Quat<double> post_elem<Quat<double>>(int, Quat<double> x) { return x; }
 
 // The seed of the scan: init[0] op init[1] op ... (identity when there is none). A sharded scan passes
 // the totals of all shards and `ninit` = its rank, so the carry needs no kernel of its own.

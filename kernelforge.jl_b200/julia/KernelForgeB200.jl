@@ -200,6 +200,11 @@ function scan!(f, op, dst::CuArray{T}, src::CuArray{T}; g=identity, tmp=nothing,
     # g is applied to every output element (src/scan/scan_kernel.jl:463,470,474); `init` is a device
     # array whose elements are folded left to right and seed the scan (one element, or the totals of
     # the shards before this one in a sharded scan)
+    if _quat_component(T) !== nothing  # Quaternion{Float32|Float64}: `*` is the Hamilton product
+        (op === (*) && f === identity && g === identity) ||
+            throw(ArgumentError("quaternion arrays support scan!(*, dst, src) with f = g = identity only"))
+        return scan_quaternion!(dst, src; tmp=tmp, Nitem=Nitem, workgroup=workgroup, init=init)
+    end
     n = length(src)
     n == 0 && return dst
     length(dst) == n || throw(ArgumentError("dst and src must have equal lengths"))
@@ -248,6 +253,36 @@ function scan!(f, op::AffineCompose, dst::CuArray{NTuple{2,Float32}}, src::CuArr
                     (CuPtr{Cfloat}, CuPtr{Cfloat}, UInt64, CuPtr{Cfloat}, UInt32, CuPtr{Cvoid}, Csize_t, Ptr{LaunchCfg}, Ptr{Cvoid}),
                     pointer(src), pointer(dst), n, init === nothing ? CU_NULL : pointer(init),
                     init === nothing ? 0 : length(init) ÷ 2, pointer(ws), length(ws), cfg_ptr(cfg), stream_handle()), "scan!")
+    end
+    dst
+end
+# Quaternions (Quaternions.jl's Quaternion{Float32|Float64}: four components s, v1, v2, v3) under `*`, the
+# reference's non-commutative scan case (test/tests/scan/scan_test.jl:22-33). Any isbits struct named
+# Quaternion with four equal Float32 or Float64 fields is accepted, so Quaternions.jl is not a dependency.
+function _quat_component(::Type{Q}) where {Q}
+    (isbitstype(Q) && nameof(Q) === :Quaternion && fieldcount(Q) == 4) || return nothing
+    C = fieldtype(Q, 1)
+    (C === Float32 || C === Float64) && all(i -> fieldtype(Q, i) === C, 2:4) ? C : nothing
+end
+function get_allocation(::Type{Scan1D}, f, op::typeof(*), src::CuArray{Q}, workgroup=nothing, blocks=nothing, arch=nothing) where {Q}
+    C = _quat_component(Q)
+    C === nothing && return _alloc(scan_bytes(Q, 0, length(src), make_cfg(workgroup, nothing, nothing)))
+    _alloc(ccall((:kf_scan_quaternion_workspace_bytes, libkf), Csize_t, (Cint, UInt64), dtype_code(C), length(src)))
+end
+function scan_quaternion!(dst::CuArray{Q}, src::CuArray{Q}; tmp=nothing, Nitem=nothing, workgroup=nothing, init=nothing) where {Q}
+    C = _quat_component(Q)
+    C === nothing && throw(ArgumentError("scan_quaternion!: element type $Q is not a Quaternion{Float32|Float64}"))
+    n = length(src)
+    n == 0 && return dst
+    cfg = make_cfg(workgroup, Nitem, nothing)
+    need = ccall((:kf_scan_quaternion_workspace_bytes, libkf), Csize_t, (Cint, UInt64), dtype_code(C), n)
+    buf = _resolve_tmp(tmp, need)
+    ws = buf.arrays.workspace
+    GC.@preserve cfg begin
+        check(ccall((:kf_scan_quaternion, libkf), Cint,
+                    (Cint, CuPtr{Cvoid}, CuPtr{Cvoid}, UInt64, CuPtr{Cvoid}, UInt32, CuPtr{Cvoid}, Csize_t, Ptr{LaunchCfg}, Ptr{Cvoid}),
+                    dtype_code(C), pointer(src), pointer(dst), n, init === nothing ? CU_NULL : pointer(init),
+                    init === nothing ? 0 : length(init), pointer(ws), length(ws), cfg_ptr(cfg), stream_handle()), "scan!")
     end
     dst
 end

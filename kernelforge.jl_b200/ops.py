@@ -10,6 +10,7 @@ operator set; the host layer recognises the supported functions by identity and 
     sqrt (as g) -> math.sqrt / sqrt
     (a, b, ...) -> a*b*...  -> prod / operator.mul     (a, b) -> (a-b)^2 -> sqdiff     (w, x) -> w*x*x -> wsq
     AffineCompose() -> the non-commutative composition of affine maps (new in this library)
+    QuaternionMul() -> the Hamilton product on [n, 4] arrays (`*` on a Quaternion array in the reference)
 
 Strings ("+", "min", "abs2", ...) are accepted as well.
 """
@@ -76,6 +77,30 @@ class AffineCompose:
 
     def __repr__(self):
         return "AffineCompose()"
+
+
+class QuaternionMul:
+    """Operator singleton: the Hamilton product of quaternions stored as [n, 4] Float32 or Float64
+    arrays of (w, x, y, z). Associative, not commutative: the operator of the reference's
+    non-commutative scan test (test/tests/scan/scan_test.jl:22-33 of KernelForge.jl, where it is `*`
+    on a QuaternionF64 array). Usable with `scan` / `scan_` only.
+    """
+
+    _inst = None
+
+    def __new__(cls):
+        if cls._inst is None:
+            cls._inst = super().__new__(cls)
+        return cls._inst
+
+    def __call__(self, l, r):
+        lw, lx, ly, lz = l
+        rw, rx, ry, rz = r
+        return (lw * rw - lx * rx - ly * ry - lz * rz, lw * rx + lx * rw + ly * rz - lz * ry,
+                lw * ry - lx * rz + ly * rw + lz * rx, lw * rz + lx * ry - ly * rx + lz * rw)
+
+    def __repr__(self):
+        return "QuaternionMul()"
 
 
 _MAPS = {identity: C.MAP_IDENTITY, abs2: C.MAP_ABS2, builtins.abs: C.MAP_ABS, operator.abs: C.MAP_ABS,

@@ -6,6 +6,7 @@ Mirrors src/scan/scan.jl:218-284 of KernelForge.jl. Calling forms:
     scan(op, src)                  scan(f, op, src)
     scan_(AffineCompose(), (a_dst, b_dst), (a_src, b_src))      # two Float32 arrays
     scan_(AffineCompose(), dst_ab, src_ab)                      # [n, 2] Float32 (NTuple{2,Float32})
+    scan_(QuaternionMul(), dst_q, src_q)                        # [n, 4] Float32 / Float64 (Quaternion{T})
 
 `g=` is applied to every output element (src/scan/scan_kernel.jl:463,470,474): identity or sqrt.
 `init=` (a device tensor of one or more elements; [k, 2] (a, b) pairs for the affine form) is folded
@@ -18,7 +19,7 @@ import torch
 
 from . import _cabi as C
 from . import ops
-from .allocations import Scan1D, resolve_tmp, scan_bytes
+from .allocations import Scan1D, quaternion_scan_bytes, resolve_tmp, scan_bytes
 
 
 def _split_args(args, n_tail):
@@ -68,6 +69,28 @@ def _scan_affine(dst, src, init, tmp, cfg):
     return dst
 
 
+def _scan_quaternion(dst, src, init, tmp, cfg):
+    ops.require_device_vector(src, "src")
+    ops.require_device_vector(dst, "dst")
+    if src.dtype not in (torch.float32, torch.float64) or dst.dtype != src.dtype or src.dim() != 2 \
+            or src.shape[1] != 4 or dst.shape != src.shape:
+        raise C.ArgumentError("QuaternionMul expects [n, 4] Float32 or Float64 arrays of (w, x, y, z)")
+    if init is not None and (init.dtype != src.dtype or init.numel() == 0 or init.numel() % 4):
+        raise C.ArgumentError("init must hold quaternions of the element type")
+    n = src.shape[0]
+    if n == 0:
+        return dst
+    code = C.F32 if src.dtype == torch.float32 else C.F64
+    buf = resolve_tmp(tmp, Scan1D, quaternion_scan_bytes(code, n), src.device)
+    with torch.cuda.device(src.device):
+        rc = C.load().kf_scan_quaternion(code, src.data_ptr(), dst.data_ptr(), n,
+                                         init.data_ptr() if init is not None else None,
+                                         init.numel() // 4 if init is not None else 0,
+                                         buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src))
+    C.check(rc, "scan!")
+    return dst
+
+
 def scan_(*args, g=ops.identity, tmp=None, Nitem=None, workgroup=None, family=None, arch=None, init=None,
           _test_hook=0):
     """`scan!([f,] op, dst, src)`: dst[i] = g(f(src[0]) op ... op f(src[i])). Returns dst (asynchronous)."""
@@ -84,6 +107,10 @@ def scan_(*args, g=ops.identity, tmp=None, Nitem=None, workgroup=None, family=No
         if init is not None and (init.dtype != torch.float32 or init.numel() == 0 or init.numel() % 2):
             raise C.ArgumentError("init must hold Float32 (a, b) pairs")
         return _scan_affine(dst, src, init, tmp, cfg)
+    if isinstance(op, ops.QuaternionMul):
+        if ops.map_code(f) != C.MAP_IDENTITY or gcode != C.POST_IDENTITY:
+            raise C.ArgumentError("QuaternionMul supports f=identity and g=identity only")
+        return _scan_quaternion(dst, src, init, tmp, cfg)
     fcode, opcode = ops.map_code(f), ops.op_code(op)
     ops.require_device_vector(src, "src")
     ops.require_device_vector(dst, "dst")

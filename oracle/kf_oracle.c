@@ -110,6 +110,44 @@ void kfo_scan_affine(const float *a, const float *b, size_t n, const double *ini
     }
 }
 
+/* accumulate(*, src) over quaternions (w, x, y, z), the Hamilton product as Quaternions.jl defines
+ * `*` (the reference's non-commutative scan test, test/tests/scan/scan_test.jl:22-33, compares with
+ * exactly this left fold on the host). Components are read as Float32 or Float64; the fold runs in
+ * Float64. init4 (one quaternion) seeds the fold from the left, or is NULL. */
+void kfo_scan_quat(const void *src, int is_f64, size_t n, const double *init4, double *out) {
+    double w = 1.0, x = 0.0, y = 0.0, z = 0.0;
+    if (init4) {
+        w = init4[0];
+        x = init4[1];
+        y = init4[2];
+        z = init4[3];
+    }
+    for (size_t i = 0; i < n; ++i) {
+        double r[4];
+        for (int k = 0; k < 4; ++k)
+            r[k] = is_f64 ? ((const double *)src)[4 * i + k] : (double)((const float *)src)[4 * i + k];
+        if (i == 0 && !init4) {
+            w = r[0];
+            x = r[1];
+            y = r[2];
+            z = r[3];
+        } else {
+            const double nw = w * r[0] - x * r[1] - y * r[2] - z * r[3];
+            const double nx = w * r[1] + x * r[0] + y * r[3] - z * r[2];
+            const double ny = w * r[2] - x * r[3] + y * r[0] + z * r[1];
+            const double nz = w * r[3] + x * r[2] - y * r[1] + z * r[0];
+            w = nw;
+            x = nx;
+            y = ny;
+            z = nz;
+        }
+        out[4 * i + 0] = w;
+        out[4 * i + 1] = x;
+        out[4 * i + 2] = y;
+        out[4 * i + 3] = z;
+    }
+}
+
 /* ---------------------------------------------------------------------------------------------
  * Integer oracle: arithmetic in the element type with wrap-around. Values travel as 64-bit
  * containers and are truncated to the element width after every step.

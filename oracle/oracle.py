@@ -42,7 +42,8 @@ def build() -> str:
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        src = os.path.join(HERE, "kf_oracle.c")
+        if not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < os.path.getmtime(src):
             build()
         L = ctypes.CDLL(LIB_PATH)
         L.kfo_max_threads.restype = c_int
@@ -53,6 +54,7 @@ def lib() -> ctypes.CDLL:
         L.kfo_scan_f32.argtypes = [c_int, c_int, c_void_p, c_size_t, POINTER(c_double), c_void_p]
         L.kfo_scan_f64.argtypes = [c_int, c_int, c_void_p, c_size_t, POINTER(c_double), c_void_p]
         L.kfo_scan_affine.argtypes = [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]
+        L.kfo_scan_quat.argtypes = [c_void_p, c_int, c_size_t, c_void_p, c_void_p]
         L.kfo_mapreduce_int.restype = c_int64
         L.kfo_mapreduce_int.argtypes = [c_int, c_int, c_int, c_void_p, c_size_t]
         L.kfo_scan_int.argtypes = [c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
@@ -114,6 +116,16 @@ def c_scan_affine(a: np.ndarray, b: np.ndarray, init=None):
     ini = _p(np.array(init, dtype=np.float64)) if init is not None else None
     lib().kfo_scan_affine(_p(a), _p(b), a.size, ini, _p(oa), _p(ob))
     return oa, ob
+
+
+def c_scan_quat(q: np.ndarray, init=None) -> np.ndarray:
+    """accumulate(*, q) for an [n, 4] Float32/Float64 array of (w, x, y, z); Float64 result."""
+    q = _c(q)
+    assert q.ndim == 2 and q.shape[1] == 4 and q.dtype in (np.float32, np.float64)
+    out = np.empty(q.shape, np.float64)
+    ini = np.array(init, dtype=np.float64) if init is not None else None
+    lib().kfo_scan_quat(_p(q), 1 if q.dtype == np.float64 else 0, q.shape[0], _p(ini) if ini is not None else None, _p(out))
+    return out
 
 
 def c_sortperm(keys: np.ndarray) -> np.ndarray:

@@ -124,6 +124,30 @@ def test_affine_fold_small_by_hand(oracle):
     assert list(oa) == [2.0, 1.0, 3.0] and list(ob) == [9.0, 3.5, 10.75]
 
 
+def test_quaternion_fold_known_products(oracle):
+    """The Hamilton product's defining identities (i*j = k, j*i = -k, i*i = j*j = k*k = i*j*k = -1),
+    which fix every sign of the product that Quaternions.jl's `*` uses, and the left-to-right order of
+    the fold (the reference's non-commutative scan test, test/tests/scan/scan_test.jl:22-33)."""
+    one, i, j, k = np.eye(4)
+    for dt in (np.float32, np.float64):
+        q = lambda *rows: np.array(rows, dtype=dt)
+        assert (oracle.c_scan_quat(q(i, j)) == [i, k]).all()
+        assert (oracle.c_scan_quat(q(j, i)) == [j, -k]).all()
+        assert (oracle.c_scan_quat(q(j, k)) == [j, i]).all()
+        assert (oracle.c_scan_quat(q(k, i)) == [k, j]).all()
+        assert (oracle.c_scan_quat(q(i, i)) == [i, -one]).all()
+        assert (oracle.c_scan_quat(q(i, j, k)) == [i, k, -one]).all()
+        assert (oracle.c_scan_quat(q(j, k), init=i) == [k, -one]).all()  # seed from the left: i*j, i*j*k
+        # (1 + 2i + 3j + 4k)(5 + 6i + 7j + 8k) = -60 + 12i + 30j + 24k
+        assert (oracle.c_scan_quat(q([1, 2, 3, 4], [5, 6, 7, 8]))[1] == [-60, 12, 30, 24]).all()
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((200, 4))
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    out = oracle.c_scan_quat(x)
+    assert np.allclose(np.linalg.norm(out, axis=1), 1.0, atol=1e-12)  # unit quaternions stay on the sphere
+    assert not np.allclose(out[-1], oracle.c_scan_quat(x[::-1].copy())[-1])  # order matters
+
+
 def test_base_like_baseline_agrees_with_oracle(oracle):
     rng = np.random.default_rng(3)
     x = rng.random(1 << 18, dtype=np.float32)

@@ -202,6 +202,86 @@ def test_affine_init_and_views(kf, oracle):
     _check_affine(n, to_host(oa), to_host(ob), ra, rb)
 
 
+def _unit_quaternions(n, seed, dtype):
+    x = np.random.default_rng(seed).standard_normal((n, 4))
+    return (x / np.linalg.norm(x, axis=1, keepdims=True)).astype(dtype)
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float64, 1e-10), (np.float32, 2e-3)])
+@pytest.mark.parametrize("n", [1, 5, 100, 1023, 1024, 1025, 100_003, 1_000_000])
+def test_quaternion_product_scan(kf, oracle, dtype, tol, n):
+    """The reference's non-commutative scan case (test/tests/scan/scan_test.jl:22-33: `*` over random
+    unit QuaternionF64, n = 10^6, against accumulate(*, src) on the host), for both component widths
+    and around the 1024-quaternion tile. Unit quaternions keep every prefix on the unit sphere, so an
+    absolute tolerance is meaningful; the Float32 bound is sqrt(n) roundings with room to spare."""
+    q = _unit_quaternions(n, n, dtype)
+    want = oracle.c_scan_quat(q)
+    got = to_host(kf.scan(kf.QuaternionMul(), to_dev(q.reshape(-1)).view(n, 4)))
+    assert got.dtype == dtype and got.shape == (n, 4)
+    assert np.abs(got.astype(np.float64) - want).max() <= tol
+    assert abs(np.linalg.norm(got[-1].astype(np.float64)) - 1.0) <= tol
+
+
+def test_quaternion_order_matters_and_is_exact_on_the_unit_group(kf, oracle):
+    """Products of +-1, +-i, +-j, +-k are exact in any precision and any association, so the scan must
+    equal the left fold bit for bit, and any swapped pair of operands would show (i*j = k, j*i = -k)."""
+    n = 300_007
+    rng = np.random.default_rng(12)
+    units = np.concatenate([np.eye(4), -np.eye(4)])
+    for dtype in (np.float32, np.float64):
+        q = units[rng.integers(0, 8, n)].astype(dtype)
+        got = to_host(kf.scan(kf.QuaternionMul(), to_dev(q.reshape(-1)).view(n, 4)))
+        assert (got.astype(np.float64) == oracle.c_scan_quat(q)).all()
+        # swapping the operands of one product flips the sign of every later prefix whenever the two
+        # factors anticommute, which half of all pairs of this group do
+        swapped = oracle.c_scan_quat(np.concatenate([q[1:2], q[0:1], q[2:]]))
+        pair = oracle.c_scan_quat(q[:2])[1], swapped[1]
+        assert (pair[0] == pair[1]).all() or (got[-1].astype(np.float64) == -swapped[-1]).all()
+
+
+def test_quaternion_init_views_and_reused_tmp(kf, oracle):
+    n = 70_001
+    q = _unit_quaternions(n, 4, np.float64)
+    init = _unit_quaternions(1, 5, np.float64)
+    want = oracle.c_scan_quat(q, init=init[0])
+    src = to_dev(q.reshape(-1)).view(n, 4)
+    dst = torch.empty_like(src)
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, kf.QuaternionMul(), src)
+    for _ in range(3):  # a stale descriptor of the call before would leak into the next one
+        kf.scan_(kf.QuaternionMul(), dst, src, init=to_dev(init.reshape(-1)), tmp=tmp)
+        assert np.abs(to_host(dst) - want).max() <= 1e-10
+    kf.scan_(kf.QuaternionMul(), src, src, tmp=tmp)  # in place
+    assert np.abs(to_host(src) - oracle.c_scan_quat(q)).max() <= 1e-10
+    # a view that starts 8 bytes into the buffer: not 16-byte aligned -> component-wise accesses
+    flat = to_dev(np.concatenate([[0.0], q.reshape(-1)]))
+    out = torch.zeros(4 * n + 1, dtype=torch.float64, device="cuda")
+    kf.scan_(kf.QuaternionMul(), out[1:].view(n, 4), flat[1:].view(n, 4))
+    assert np.abs(to_host(out)[1:].reshape(n, 4) - oracle.c_scan_quat(q)).max() <= 1e-10
+    assert to_host(out)[0] == 0.0
+    with pytest.raises(kf.ArgumentError):
+        kf.scan(kf.QuaternionMul(), torch.ones(12, dtype=torch.float32, device="cuda").view(4, 3))
+    with pytest.raises(kf.ArgumentError):
+        kf.scan(kf.abs2, kf.QuaternionMul(), src)
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.identity, kf.QuaternionMul(), src)  # not commutative: scan only
+
+
+def test_quaternion_bounded_wait_runs_out(kf, oracle):
+    """Eight self-validating descriptor words per tile: a silent tile still ends in KF_ERR_TIMEOUT, and
+    the workspace serves the next call."""
+    from kernelforge_jl_b200 import _cabi as C
+    n = 30 * 1024 + 7
+    q = _unit_quaternions(n, 6, np.float64)
+    src = to_dev(q.reshape(-1)).view(n, 4)
+    dst = torch.empty_like(src)
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, kf.QuaternionMul(), src)
+    kf.scan_(kf.QuaternionMul(), dst, src, tmp=tmp, _test_hook=((1 + 3) << 16) | 400)
+    assert kf.lib.kf_check(tmp.ptr(), None) == C.ERR_TIMEOUT
+    kf.scan_(kf.QuaternionMul(), dst, src, tmp=tmp)
+    assert kf.lib.kf_check(tmp.ptr(), None) == C.OK
+    assert np.abs(to_host(dst) - oracle.c_scan_quat(q)).max() <= 1e-10
+
+
 def test_errors(kf):
     x = torch.ones(100, dtype=torch.float32, device="cuda")
     with pytest.raises(kf.ArgumentError):
@@ -213,7 +293,9 @@ def test_errors(kf):
     small = kf.KernelBuffer(kf.Scan1D, torch.empty(64, dtype=torch.uint8, device="cuda"))
     with pytest.raises(kf.KernelForgeError):
         kf.scan("+", x, tmp=small)
-    assert kf.lib.kf_check(kf.get_allocation(kf.Scan1D, kf.identity, "+", x).ptr(), None) >= 0
+    tmp = kf.get_allocation(kf.Scan1D, kf.identity, "+", x)
+    kf.scan("+", x, tmp=tmp)
+    assert kf.lib.kf_check(tmp.ptr(), None) == 0  # (a workspace no call has used yet holds no status)
 
 
 def test_full_size_2p28_uint32(kf):
