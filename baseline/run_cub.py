@@ -9,7 +9,7 @@ and recomputes GB/s from their `mean_ms` with the byte counts this repository us
 reduce n*sizeof(T), scan 2*n*sizeof(T), 8-bit-digit radix sort (2P+1)*n*sizeof(K). (The harnesses'
 own `throughput_gb_s` uses other conventions: GiB, and 2*N*sizeof(T) for sorts.)
 
-    python baseline/run_cub.py [--log2n 28] [--iters 20] [--out FILE]
+    python baseline/run_cub.py [--log2n 28 | --n 100000000] [--iters 20] [--out FILE]
 """
 import argparse
 import json
@@ -72,11 +72,12 @@ def find_mean_ms(obj):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--log2n", type=int, default=28)
+    ap.add_argument("--n", type=int, default=0, help="an exact element count instead of 2^log2n (the reference publishes 10^6, 10^7, 10^8)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup-ms", type=int, default=200)
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
-    n = 1 << args.log2n
+    n = args.n if args.n else 1 << args.log2n
     rows = []
     for binary, extra, label, bpe in CASES:
         exe = os.path.join(REF, binary)

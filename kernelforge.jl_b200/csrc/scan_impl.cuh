@@ -131,24 +131,33 @@ struct AffineSoaAccess {
     }
 };
 
-// Quaternions as an array of structs: a slot is one quaternion (one 16-byte vector for Float32
-// components, two for Float64).
+// Quaternions as an array of structs. Float32 components: a slot is FOUR consecutive quaternions of one
+// lane (64 bytes), which the lane scans serially, so that only the slot totals go through the warp scan
+// (measured at n = 2^24: 0.375 ms against 0.457 ms with one quaternion per slot); a lane's vectors are
+// 64 bytes apart from its neighbour's, so these loads go through L1. Float64 components: one quaternion
+// (two 16-byte vectors) per slot, streaming accesses (0.865 ms against 0.944 ms with four per slot).
 template <typename F> struct QuatAccess {
-    static constexpr int EPV = 1;
+    static constexpr int EPV = sizeof(F) == 4 ? 4 : 1;
     using Q = Quat<F>;
+    static constexpr int NV = (int)(EPV * sizeof(Q) / 16);  // 16-byte vectors per slot
     const Q *src;
     Q *dst;
-    __device__ __forceinline__ void load_slot(u64 i, Q (&e)[1]) const {
-        uint4 v[sizeof(Q) / 16];
+    __device__ __forceinline__ void load_slot(u64 i0, Q (&e)[EPV]) const {
+        uint4 v[NV];
+        const uint4 *p = reinterpret_cast<const uint4 *>(src + i0);
 #pragma unroll
-        for (int k = 0; k < (int)(sizeof(Q) / 16); ++k) v[k] = ld_v4(reinterpret_cast<const uint4 *>(src + i) + k);
-        memcpy(&e[0], v, sizeof(Q));
+        for (int k = 0; k < NV; ++k) v[k] = EPV == 1 ? ld_v4(p + k) : p[k];
+        memcpy(&e[0], v, sizeof(v));
     }
-    __device__ __forceinline__ void store_slot(u64 i, const Q (&e)[1]) const {
-        uint4 v[sizeof(Q) / 16];
-        memcpy(v, &e[0], sizeof(Q));
+    __device__ __forceinline__ void store_slot(u64 i0, const Q (&e)[EPV]) const {
+        uint4 v[NV];
+        memcpy(v, &e[0], sizeof(v));
+        uint4 *p = reinterpret_cast<uint4 *>(dst + i0);
 #pragma unroll
-        for (int k = 0; k < (int)(sizeof(Q) / 16); ++k) st_stream_v4(reinterpret_cast<uint4 *>(dst + i) + k, v[k]);
+        for (int k = 0; k < NV; ++k) {
+            if (EPV == 1) st_stream_v4(p + k, v[k]);
+            else p[k] = v[k];
+        }
     }
     __device__ __forceinline__ Q load_elem(u64 i) const {
         const F *p = reinterpret_cast<const F *>(src + i);

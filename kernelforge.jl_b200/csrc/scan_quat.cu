@@ -7,7 +7,7 @@
 
 namespace kf {
 
-constexpr int kQuatThreads = 256, kQuatPerThread = 4;
+constexpr int kQuatThreads = 256, kQuatPerThread = 4;  // as kQuatPerThread / EPV slots of EPV quaternions
 constexpr u64 kQuatTile = (u64)kQuatThreads * kQuatPerThread;
 
 static size_t quat_ws_bytes(int comp_bytes, u64 n, u64 *ntiles) {
@@ -19,7 +19,7 @@ template <typename F>
 static int quat_launch(const void *src, void *dst, const ScanArgs &a, cudaStream_t s) {
     using Q = Quat<F>;
     QuatAccess<F> acc{static_cast<const Q *>(src), static_cast<Q *>(dst)};
-    scan_kernel<Q, OpQuatMul, QuatAccess<F>, kQuatThreads, kQuatPerThread><<<(unsigned)a.ntiles, kQuatThreads, 0, s>>>(acc, a);
+    scan_kernel<Q, OpQuatMul, QuatAccess<F>, kQuatThreads, kQuatPerThread / QuatAccess<F>::EPV><<<(unsigned)a.ntiles, kQuatThreads, 0, s>>>(acc, a);
     note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     return KF_OK;

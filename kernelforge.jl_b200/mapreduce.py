@@ -48,7 +48,7 @@ def _mapreduce_tuple(f, op, dst, srcs, g, tmp, cfg):
         raise C.ArgumentError("reducing over an empty collection is not allowed")
     buf = resolve_tmp(tmp, MapReduce1D, mapreduce_bytes(first, cfg), first.device)
     ptrs = (ctypes.c_void_p * len(srcs))(*[t.data_ptr() for t in srcs])
-    with torch.cuda.device(first.device):
+    with ops.on_device(first.device):
         rc = C.load().kf_mapreduce_multi(fcode, opcode, gcode, ops.dtype_code(first), ptrs, len(srcs), n, dst.data_ptr(),
                                          buf.ptr(), buf.nbytes, cfg, ops.stream_handle(first))
     C.check(rc, "mapreduce")
@@ -76,7 +76,7 @@ def mapreduce_(f, op, dst, src, *, dims=None, g=ops.identity, tmp=None, Nitem=No
         raise C.ArgumentError("reducing over an empty collection is not allowed")
     cfg = C.make_cfg(workgroup, Nitem, blocks)
     buf = resolve_tmp(tmp, MapReduce1D, mapreduce_bytes(src, cfg), src.device)
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = C.load().kf_mapreduce(fcode, opcode, gcode, ops.dtype_code(src), src.data_ptr(), n, dst.data_ptr(),
                                    buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src))
     C.check(rc, "mapreduce")

@@ -17,6 +17,7 @@ Strings ("+", "min", "abs2", ...) are accepted as well.
 from __future__ import annotations
 
 import builtins
+import contextlib
 import math
 import operator
 
@@ -175,5 +176,22 @@ def require_device_vector(t, name: str) -> None:
         raise C.ArgumentError("%s must be contiguous (dense views only)" % name)
 
 
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def on_device(device):
+    """Context in which `device` is the current CUDA device. The common case, where it already is,
+    costs one query instead of torch's save / set / restore sequence."""
+    if device.index is None or torch.cuda.current_device() == device.index:
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_handle(t: torch.Tensor) -> int:
+    """The cudaStream_t of torch's current stream on the tensor's device."""
+    if _raw_stream is not None and t.device.index is not None:
+        return _raw_stream(t.device.index)  # one C call; torch.cuda.current_stream builds a Stream object (~7 us)
     return torch.cuda.current_stream(t.device).cuda_stream

@@ -45,7 +45,7 @@ def _scan_affine(dst, src, init, tmp, cfg):
         if n == 0:
             return dst
         buf = resolve_tmp(tmp, Scan1D, scan_bytes(C.F32, True, n, cfg), src[0].device)
-        with torch.cuda.device(src[0].device):
+        with ops.on_device(src[0].device):
             rc = lib.kf_scan_affine_soa(src[0].data_ptr(), src[1].data_ptr(), dst[0].data_ptr(), dst[1].data_ptr(),
                                         n, init.data_ptr() if init is not None else None,
                                         init.numel() // 2 if init is not None else 0,
@@ -61,7 +61,7 @@ def _scan_affine(dst, src, init, tmp, cfg):
     if n == 0:
         return dst
     buf = resolve_tmp(tmp, Scan1D, scan_bytes(C.F32, True, n, cfg), src.device)
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = lib.kf_scan_affine_aos(src.data_ptr(), dst.data_ptr(), n, init.data_ptr() if init is not None else None,
                                     init.numel() // 2 if init is not None else 0,
                                     buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src))
@@ -82,7 +82,7 @@ def _scan_quaternion(dst, src, init, tmp, cfg):
         return dst
     code = C.F32 if src.dtype == torch.float32 else C.F64
     buf = resolve_tmp(tmp, Scan1D, quaternion_scan_bytes(code, n), src.device)
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = C.load().kf_scan_quaternion(code, src.data_ptr(), dst.data_ptr(), n,
                                          init.data_ptr() if init is not None else None,
                                          init.numel() // 4 if init is not None else 0,
@@ -125,7 +125,7 @@ def scan_(*args, g=ops.identity, tmp=None, Nitem=None, workgroup=None, family=No
         return dst
     code = ops.dtype_code(src)
     buf = resolve_tmp(tmp, Scan1D, scan_bytes(code, False, n, cfg), src.device)
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = C.load().kf_scan(fcode, opcode, gcode, code, src.data_ptr(), dst.data_ptr(), n,
                               init.data_ptr() if init is not None else None, init.numel() if init is not None else 0,
                               buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src))

@@ -58,7 +58,7 @@ def argmax1d(f, rel, src, *, to_cpu=True, with_value=False, tmp=None):
     ws = tmp if tmp is not None else torch.empty(need, dtype=torch.uint8, device=src.device)
     idx = torch.empty(1, dtype=torch.int64, device=src.device)
     val = torch.empty(1, dtype=src.dtype, device=src.device)
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = lib.kf_argmax(ops.map_code(f), greater, code, src.data_ptr(), n, val.data_ptr(), idx.data_ptr(), ws.data_ptr(),
                            ws.numel(), ops.stream_handle(src))
     C.check(rc, "argmax")
@@ -87,7 +87,7 @@ def _find(pred, src, last):
     code = ops.dtype_code(src)
     keep, ptr = _host_scalar(code, pred.value)
     out = torch.empty(1, dtype=torch.int64, device=src.device)
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = C.load().kf_find(pred.code, 1 if last else 0, code, src.data_ptr(), n, ptr, out.data_ptr(), ops.stream_handle(src))
     C.check(rc, "findfirst")
     r = int(out.cpu()[0])
@@ -112,7 +112,7 @@ def vcopy_(dst, src):
     ops.require_device_vector(dst, "dst")
     if dst.dtype != src.dtype or dst.numel() != src.numel():
         raise C.ArgumentError("dst and src must have the same element type and length")
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = C.load().kf_vcopy(dst.data_ptr(), src.data_ptr(), src.numel() * src.element_size(), ops.stream_handle(src))
     C.check(rc, "vcopy!")
     return dst
@@ -123,7 +123,7 @@ def setvalue_(dst, value):
     ops.require_device_vector(dst, "dst")
     code = ops.dtype_code(dst)
     keep, ptr = _host_scalar(code, value)
-    with torch.cuda.device(dst.device):
+    with ops.on_device(dst.device):
         rc = C.load().kf_setvalue(code, dst.data_ptr(), dst.numel(), ptr, ops.stream_handle(dst))
     C.check(rc, "setvalue!")
     return dst

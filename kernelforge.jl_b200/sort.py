@@ -59,7 +59,7 @@ def sort_(*args, keys=None, keys_dst=None, by=None, uint_map=None, lt=None, rev=
         if n == 0:
             return dst
         buf = resolve_tmp(tmp, Sort1D, sort_bytes(code, 0, n, cfg), src.device)
-        with torch.cuda.device(src.device):
+        with ops.on_device(src.device):
             rc = lib.kf_sort_keys(code, src.data_ptr(), dst.data_ptr(), n, buf.ptr(), buf.nbytes, cfg,
                                   ops.stream_handle(src))
         C.check(rc, "sort!")
@@ -82,7 +82,7 @@ def sort_(*args, keys=None, keys_dst=None, by=None, uint_map=None, lt=None, rev=
     if n == 0:
         return dst, keys_dst
     buf = resolve_tmp(tmp, Sort1D, sort_bytes(kcode, vb, n, cfg), src.device)
-    with torch.cuda.device(src.device):
+    with ops.on_device(src.device):
         rc = lib.kf_sort_pairs(kcode, keys.data_ptr(), keys_dst.data_ptr(), vb, src.data_ptr(), dst.data_ptr(), n,
                                buf.ptr(), buf.nbytes, cfg, ops.stream_handle(src))
     C.check(rc, "sort!")
@@ -104,7 +104,7 @@ def sortperm(keys, **kwargs):
     wide = n >= 2 ** 31
     idx = torch.empty(n, dtype=torch.int64 if wide else torch.int32, device=keys.device)
     if n:
-        with torch.cuda.device(keys.device):
+        with ops.on_device(keys.device):
             rc = C.load().kf_iota(C.I64 if wide else C.I32, idx.data_ptr(), n, 0, ops.stream_handle(keys))
         C.check(rc, "sortperm")
     out, _ = sort_(torch.empty_like(idx), idx, keys=keys, keys_dst=torch.empty_like(keys), **kwargs)

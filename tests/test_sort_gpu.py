@@ -77,6 +77,16 @@ def test_one_byte_keys_runs_path(kf, oracle, dtype):
     assert_same_bits(to_host(keys_sorted), to_host(kf.sort(to_dev(x))))
 
 
+@pytest.mark.parametrize("n", [1, 33, 10_001, 1_000_000])
+def test_bool_input(kf, n):
+    """Bool arrays sort as bytes (test/tests/sort/sort_test.jl:183-193 of KernelForge.jl: `rand(Bool, n)`
+    against Base.sort): all false before all true, and the same count of each."""
+    x = np.random.default_rng(n).integers(0, 2, n).astype(np.bool_)
+    y = kf.sort(torch.from_numpy(x).cuda())
+    assert y.dtype == torch.bool
+    assert (y.cpu().numpy() == np.sort(x)).all()
+
+
 @pytest.mark.parametrize("dtype", [np.uint16, np.int16])
 def test_two_byte_keys_runs_path(kf, oracle, dtype):
     """Two-byte keys without payload, from 2^22 keys on, are written out as the 65 536 runs of their
