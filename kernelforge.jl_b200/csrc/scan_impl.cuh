@@ -214,6 +214,33 @@ template <typename T, typename Op> __device__ __forceinline__ T fold_init(const 
 }
 
 
+// Sixteen packed bytes: their sum (the low 8 bits are the wrap-around sum), and their inclusive
+// wrap-around prefix sums on top of a carried-in byte `b`. A word {b0,b1,b2,b3} is split into its even
+// and odd bytes as two 16-bit lanes each; lane sums stay below 2^16, so nothing carries between lanes:
+//   lo = {b0, b2}, hi = {b1, b3};  lo * 0x00010001 = {b0, b0+b2};
+//   even prefixes {p0, p2} = {b0, b0+b2} + {0, b1} + b;  odd prefixes {p1, p3} = {b0, b0+b2} + {b1, b1+b3} + b.
+__device__ __forceinline__ u32 byte_sum16(uint4 r) {
+    u32 s = __dp4a(r.x, 0x01010101u, 0u);
+    s = __dp4a(r.y, 0x01010101u, s);
+    s = __dp4a(r.z, 0x01010101u, s);
+    return __dp4a(r.w, 0x01010101u, s);
+}
+__device__ __forceinline__ uint4 byte_prefix16(uint4 r, u32 b) {
+    u32 carry = b | (b << 16);  // the carried-in byte in both lanes
+    u32 w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const u32 lo = __byte_perm(w[i], 0u, 0x4240u);  // {b0, 0, b2, 0}
+        const u32 hi = __byte_perm(w[i], 0u, 0x4341u);  // {b1, 0, b3, 0}
+        const u32 s_lo = lo * 0x00010001u + carry;
+        const u32 even = (hi << 16) + s_lo;
+        const u32 odd = hi * 0x00010001u + s_lo;
+        w[i] = __byte_perm(even, odd, 0x6240u);          // {p0, p1, p2, p3}, low bytes of the lanes
+        carry = __byte_perm(odd, 0u, 0x4242u);           // p3 in both lanes
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Scans the VECS x EPV elements a thread holds (in place, inclusive within each slot) and the slot
 // totals across the warp. On return e[j][k] is inclusive within its slot, slot_excl[j] is the
 // combination of everything the warp holds before slot j of this lane, and the return value is

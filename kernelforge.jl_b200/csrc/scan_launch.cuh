@@ -41,13 +41,18 @@ inline u64 scan_tile_elems(int variant, int epv, int narr) {
 
 int scan_plan(int elem_bytes, int epv, int narr, u64 n, const kf_launch_cfg *cfg, ScanPlan *plan);
 
-template <typename T, typename Op, typename Access, typename Arrays, int THREADS, int VECS, int NBUF, int K, int LAG>
+template <typename T, typename Op, typename Access, typename Arrays, int THREADS, int VECS, int NBUF, int K, int LAG, bool PACKED = false>
 int scan_launch_ring_one(const Access &acc, const Arrays &arr, const ScanArgs &args, cudaStream_t s) {
     constexpr int DEPTH = 8, NRES = 1;  // one resolver warp, 256 descriptors per round trip
     using SM = ScanRolesSmem<Arrays, T, THREADS, VECS, NBUF, K>;
     static_assert(SM::kBytes <= 227 * 1024, "ring does not fit in shared memory");
     constexpr int CTA = THREADS + 32 + 32 * NRES;
-    auto kern = scan_kernel_roles<T, Op, Access, Arrays, THREADS, VECS, NBUF, K, DEPTH, NRES, LAG>;
+    // One-byte `+` with no maps takes the packed instantiation of the kernel.
+    if constexpr (!PACKED && sizeof(T) == 1 && std::is_same<Op, OpAdd>::value && Arrays::NARR == 1) {
+        if (args.f == KF_MAP_IDENTITY && args.g == KF_POST_IDENTITY)
+            return scan_launch_ring_one<T, Op, Access, Arrays, THREADS, VECS, NBUF, K, LAG, true>(acc, arr, args, s);
+    }
+    auto kern = scan_kernel_roles<T, Op, Access, Arrays, THREADS, VECS, NBUF, K, DEPTH, NRES, LAG, PACKED>;
     KF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes));
     // One CTA per SM: the look-ahead distance K is tuned for tiles of that size arriving at that rate.
     u64 grid = (u64)device_sm_count();

@@ -104,8 +104,15 @@ template <typename T, typename Op> __device__ __forceinline__ T warp_fold_ascend
     }
 }
 
-template <typename T, typename Op, typename Access, typename Arrays, int THREADS, int VECS, int NBUF, int K, int DEPTH, int NRES, int LAG>
+template <typename T, typename Op, typename Access, typename Arrays, int THREADS, int VECS, int NBUF, int K, int DEPTH, int NRES, int LAG,
+          bool PACKED = false>
 __global__ void __launch_bounds__(THREADS + 32 + 32 * NRES) scan_kernel_roles(Access acc, Arrays arr, ScanArgs args) {
+    // PACKED: one-byte elements under `+` (wrap-around, so signed and unsigned alike) with f = g =
+    // identity stay packed, four elements per register: sums by dp4a, prefixes in two 16-bit lanes per
+    // word (byte_sum16 / byte_prefix16). It is an instantiation of its own because the per-element
+    // code needs a register per BYTE (64 to 128 of them), costs 11.6 instructions per element and is
+    // issue-bound at 0.68 of the copy rate.
+    static_assert(!PACKED || (sizeof(T) == 1 && std::is_same<Op, OpAdd>::value && Arrays::NARR == 1), "PACKED is the byte-add form");
     using SM = ScanRolesSmem<Arrays, T, THREADS, VECS, NBUF, K>;
     constexpr int EPV = Arrays::EPV;
     constexpr int NARR = Arrays::NARR;
@@ -386,14 +393,18 @@ __global__ void __launch_bounds__(THREADS + 32 + 32 * NRES) scan_kernel_roles(Ac
                     const u32 slot = warp_slot0 + v * 32 + lane;
 #pragma unroll
                     for (int a = 0; a < NARR; ++a) raw[a] = *reinterpret_cast<const uint4 *>(buf + a * SM::ARR_BYTES + slot * 16);
-                    Arrays::unpack(raw, e);
-                    if (args.f != KF_MAP_IDENTITY) {
+                    if constexpr (PACKED) {
+                        rowsum[v] = (T)byte_sum16(raw[0]);
+                    } else {
+                        Arrays::unpack(raw, e);
+                        if (args.f != KF_MAP_IDENTITY) {
 #pragma unroll
-                        for (int k = 0; k < EPV; ++k) e[k] = map_elem<T>(args.f, e[k]);
+                            for (int k = 0; k < EPV; ++k) e[k] = map_elem<T>(args.f, e[k]);
+                        }
+                        rowsum[v] = e[0];
+#pragma unroll
+                        for (int k = 1; k < EPV; ++k) rowsum[v] = Op::template apply<T>(rowsum[v], e[k]);
                     }
-                    rowsum[v] = e[0];
-#pragma unroll
-                    for (int k = 1; k < EPV; ++k) rowsum[v] = Op::template apply<T>(rowsum[v], e[k]);
                 }
             } else {
 #pragma unroll
@@ -442,6 +453,51 @@ __global__ void __launch_bounds__(THREADS + 32 + 32 * NRES) scan_kernel_roles(Ac
             if (tile >= args.ntiles) break;
             const u64 start = s_start[q], count = s_count[q];
             const bool fast = count == TILE;
+            if constexpr (PACKED) {
+                // the ragged last tile builds its vectors from single bytes (zeros past the end)
+                uint4 rv[VECS];
+#pragma unroll
+                for (int v = 0; v < VECS; ++v) {
+                    const u64 off0 = (u64)(warp_slot0 + v * 32 + lane) * 16;
+                    if (fast) {
+                        rv[v] = ld_v4(arr.src[0] + start + off0);
+                    } else {
+                        u32 w[4] = {0, 0, 0, 0};
+#pragma unroll
+                        for (int k = 0; k < 16; ++k)
+                            if (off0 + k < count) w[k >> 2] |= (u32)(uint8_t)acc.load_elem(start + off0 + k) << (8 * (k & 3));
+                        rv[v] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+                if (more) {
+                    const int rr = reduce_step(s + K);
+                    more = rr == 0;
+                    if (rr == 2) break;
+                }
+                T tot[VECS][1], slot_excl[VECS];
+#pragma unroll
+                for (int v = 0; v < VECS; ++v) tot[v][0] = (T)byte_sum16(rv[v]);
+                (void)warp_tile_scan<T, Op, VECS, 1>(tot, slot_excl, lane);
+                if (!mbar_wait_or_abort_warp(&s_base[q], (s / NSTEP) & 1, s_abort)) {
+                    if (lane == 0) wait_failed(0xFFFFFFFAu);
+                    break;
+                }
+                const T base = Op::template apply<T>(slot_ref(&s_tile_excl[q]), slot_ref(&s_warp_excl[q * WARPS + warp]));
+#pragma unroll
+                for (int v = 0; v < VECS; ++v) {
+                    const u64 off0 = (u64)(warp_slot0 + v * 32 + lane) * 16;
+                    const uint4 o = byte_prefix16(rv[v], (u32)(uint8_t)Op::template apply<T>(base, slot_excl[v]));
+                    if (fast) {
+                        st_stream_v4(arr.dst[0] + start + off0, o);
+                    } else {
+                        const u32 w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                        for (int k = 0; k < 16; ++k)
+                            if (off0 + k < count) acc.store_elem(start + off0 + k, (T)(w[k >> 2] >> (8 * (k & 3))));
+                    }
+                }
+                continue;
+            }
             T e[VECS][EPV];
             if (fast) {
 #pragma unroll

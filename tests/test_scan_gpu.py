@@ -202,6 +202,41 @@ def test_affine_init_and_views(kf, oracle):
     _check_affine(n, to_host(oa), to_host(ob), ra, rb)
 
 
+@pytest.mark.parametrize("workgroup,nitem", [(768, 4), (384, 8), (512, 8)])
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8])
+def test_one_byte_add_packed_path(kf, oracle, dtype, workgroup, nitem):
+    """One-byte `+` with no maps runs a packed instantiation of the persistent kernel (four elements per
+    register): sizes around its tile (threads x vectors x 16 bytes), a ragged last tile, a misaligned
+    view (short head tile), in place, a left seed, saturated inputs (every carry between the packed
+    lanes), and the mapped form, which keeps the per-element code."""
+    tile = workgroup * nitem * 16
+    rng = np.random.default_rng(tile)
+    info = np.iinfo(dtype)
+    for n in (tile - 1, tile, tile + 1, 2 * tile + 17, 40 * tile + 12_345):
+        for x in (rng.integers(info.min, info.max, n, dtype=dtype, endpoint=True), np.full(n, info.max, dtype=dtype),
+                  np.full(n, info.min, dtype=dtype)):
+            _check_scan(kf, oracle, x, "+", workgroup=workgroup, Nitem=nitem)
+    n = 9 * tile + 4321
+    x = rng.integers(info.min, info.max, n + 16, dtype=dtype, endpoint=True)
+    for off in (1, 5, 15):
+        src = to_dev(x)[off:off + n]
+        dst = torch.zeros(n + 32, dtype=src.dtype, device="cuda")
+        kf.scan_("+", dst[off:off + n], src, workgroup=workgroup, Nitem=nitem)
+        got = to_host(dst)
+        assert (got[off:off + n] == oracle.c_scan(0, OPC["+"], x[off:off + n])).all()
+        assert not got[:off].any() and not got[off + n:].any()
+    buf = to_dev(x[:n])
+    kf.scan_("+", buf, buf, workgroup=workgroup, Nitem=nitem)  # in place
+    assert (to_host(buf) == oracle.c_scan(0, OPC["+"], x[:n])).all()
+    seed = np.array([info.max, 3], dtype=dtype)
+    got = to_host(kf.scan("+", to_dev(x[:n]), init=to_dev(seed), workgroup=workgroup, Nitem=nitem))
+    want = (np.cumsum(x[:n].astype(np.int64)) + int(seed.astype(np.int64).sum())).astype(dtype)
+    assert (got == want).all()
+    if dtype == np.int8:
+        got = to_host(kf.scan(kf.abs2, "+", to_dev(x[:n]), workgroup=workgroup, Nitem=nitem))
+        assert (got == oracle.c_scan(oracle.MAP_ABS2, OPC["+"], x[:n])).all()
+
+
 def _unit_quaternions(n, seed, dtype):
     x = np.random.default_rng(seed).standard_normal((n, 4))
     return (x / np.linalg.norm(x, axis=1, keepdims=True)).astype(dtype)
