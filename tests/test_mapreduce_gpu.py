@@ -66,6 +66,31 @@ def test_integer_ops_exact(kf, oracle, dtype, op):
         assert int(got) == int(ref), (n, got, ref)
 
 
+@pytest.mark.parametrize("dtype", [np.uint8, np.int8])
+def test_one_byte_sum_packed_path(kf, oracle, dtype):
+    """One-byte `+` without a map sums whole strips with packed arithmetic (four bytes per dp4a, 32-bit
+    running sums taken modulo 256 at the end): sizes around a strip, large inputs, saturated inputs,
+    misaligned views, every launch variant; with a map the per-element code runs."""
+    rng = np.random.default_rng(41)
+    info = np.iinfo(dtype)
+    for n in (1, 15, 16, 16_383, 16_384, 16_385, 1_000_003, 50_000_001):
+        for x in (rng.integers(info.min, info.max, n, dtype=dtype, endpoint=True), np.full(n, info.max, dtype=dtype),
+                  np.full(n, info.min, dtype=dtype)):
+            want = int(oracle.c_mapreduce(oracle.MAP_IDENTITY, NP_OPS["+"], x))
+            assert int(kf.mapreduce(kf.identity, "+", to_dev(x))) == want, n
+    x = rng.integers(info.min, info.max, 3_000_017, dtype=dtype, endpoint=True)
+    for off in (1, 7, 15):
+        want = int(oracle.c_mapreduce(oracle.MAP_IDENTITY, NP_OPS["+"], x[off:]))
+        assert int(kf.mapreduce(kf.identity, "+", to_dev(x)[off:])) == want
+    for workgroup, nitem in ((256, 4), (512, 4), (256, 8)):
+        for blocks in (1, 148, 1184):
+            got = kf.mapreduce(kf.identity, "+", to_dev(x), workgroup=workgroup, Nitem=nitem, blocks=blocks)
+            assert int(got) == int(oracle.c_mapreduce(oracle.MAP_IDENTITY, NP_OPS["+"], x))
+    if dtype == np.int8:
+        got = kf.mapreduce(kf.abs2, "+", to_dev(x))
+        assert int(got) == int(oracle.c_mapreduce(oracle.MAP_ABS2, NP_OPS["+"], x))
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("f,op", [("identity", "+"), ("abs2", "+"), ("abs", "max"), ("identity", "min"),
                                   ("identity", "max"), ("identity", "*")])
