@@ -7,7 +7,8 @@ Headline workload (one "step"): the single-GPU scan configuration the metric is 
 inclusive `scan!(+)` over Float32 n=2^28 (x ~ U[0,1)) and over UInt32 n=2^28 (x ~ U{0..255}),
 i.e. 2 * 8n = 4.29 GB of algorithmic traffic per GPU per step. With N > 1 every rank holds its own
 2^28-element shard of one global array of N*2^28 elements (weak scaling); a step is the sharded
-scan: local reduce, NCCL allgather of the shard totals, local scan seeded with the carry.
+scan: local reduce, exchange of the shard totals (a kernel of the library over mapped peer memory), local
+scan seeded with the totals of the shards before.
 
 `value` is whole-job effective GB/s (algorithmic bytes / device time) with the inputs resident in
 HBM; `e2e` is the same metric through the host-buffer API (pinned host arrays in, host arrays out,
@@ -46,7 +47,7 @@ def workload_config(world):
     n = N_HEADLINE
     return {"workload": "inclusive scan!(+, dst, x): Float32 x~U[0,1) n=2^28 and UInt32 x~U{0..255} n=2^28 "
                         "per GPU" + ("" if world == 1 else "; sharded over %d GPUs (global n=%d*2^28): local "
-                                     "reduce, NCCL allgather of the shard totals, seeded local scan" % (world, world)),
+                                     "reduce, exchange of the shard totals over mapped peer memory, seeded local scan" % (world, world)),
             "n_per_gpu": n, "algorithmic_bytes_per_step": world * 2 * 8 * n,
             "l2": "inputs (1 GiB per array) are larger than the 126 MB L2; no flush needed"}
 
