@@ -5,6 +5,7 @@
 #include "launch_table.h"
 
 #include <atomic>
+#include <cstdlib>
 #include <string.h>
 
 namespace kf {
@@ -12,6 +13,13 @@ namespace kf {
 static thread_local int g_last_cuda_error = 0;
 static std::atomic<unsigned long long> g_launches{0};
 void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+bool log_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("KF_LOG");
+        return e && e[0] && e[0] != '0';
+    }();
+    return on;
+}
 void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = (int)e; }
 
 // SM count of the current device; 148 (B200) when no device can be queried, so that size queries

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <cstdio>
 #include <stdint.h>
 #include <stddef.h>
 
@@ -320,5 +321,16 @@ int device_sm_count();
 
 // Counts one kernel launch of this library (process-wide, read by kf_launch_count).
 void note_launch();
+// KF_LOG=1 in the environment: one line per library call on stderr with the launch geometry that the
+// table (or the caller's kf_launch_cfg) chose. Read once per process.
+bool log_enabled();
+#define KF_LOGF(...)                          \
+    do {                                      \
+        if (kf::log_enabled()) {              \
+            std::fprintf(stderr, "[kf] ");    \
+            std::fprintf(stderr, __VA_ARGS__); \
+            std::fprintf(stderr, "\n");       \
+        }                                     \
+    } while (0)
 
 }  // namespace kf

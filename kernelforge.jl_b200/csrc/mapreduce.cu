@@ -234,6 +234,8 @@ extern "C" int32_t kf_mapreduce(int32_t f, int32_t op, int32_t g, int32_t dtype,
     if (rc != KF_OK) return rc;
     const size_t need = kHeaderBytes + align_up((size_t)blocks * eb, 256);
     if (ws_bytes < need) return KF_ERR_WORKSPACE_TOO_SMALL;
+    KF_LOGF("mapreduce f=%d op=%d g=%d dtype=%d n=%llu: %dx%d, %d CTAs", f, op, g, dtype, (unsigned long long)n,
+            kMrVariants[variant].threads, kMrVariants[variant].unroll, blocks);
 
     cudaStream_t s = (cudaStream_t)stream;
     u32 *header = (u32 *)ws;

@@ -106,6 +106,9 @@ extern "C" int32_t kf_scan(int32_t f, int32_t op, int32_t g, int32_t dtype, cons
     a.spin_limit = test_spin_limit(cfg);
     a.mute_tile = test_mute_tile(cfg);
     cudaStream_t s = (cudaStream_t)stream;
+    KF_LOGF("scan f=%d op=%d g=%d dtype=%d n=%llu: %dx%d %s kernel, %llu tiles, head %llu, vectors %d", f, op, g, dtype,
+            (unsigned long long)n, kScanVariants[p.variant].threads, kScanVariants[p.variant].vecs,
+            kScanVariants[p.variant].ring ? "persistent" : "direct", (unsigned long long)a.ntiles, (unsigned long long)a.head, a.vec_ok);
     KF_CUDA_TRY(cudaMemsetAsync(ws, 0, kHeaderBytes + a.ntiles * p.words * 8, s));
     switch (dtype) {
     case KF_U8: return scan_dispatch_u8(op, p.variant, src, dst, a, s);

@@ -296,6 +296,11 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
     // histogram, 256-bin scan, runs written out. In place works as it is: the histogram has read src
     // before the fill starts.
     const bool byte_runs = k.bytes == 1 && val_bytes == 0 && test_mute_tile(cfg) == 0;
+    KF_LOGF("sort key bytes=%d float=%d payload bytes=%d n=%llu: %s, %dx%d, %llu tiles", k.bytes, (int)k.is_float, val_bytes,
+            (unsigned long long)n,
+            byte_runs ? "256 runs written out" : (k.bytes == 2 && val_bytes == 0 && n >= kShortRunsMinN && test_mute_tile(cfg) == 0)
+                                                     ? "65536 runs written out" : "onesweep passes",
+            kSortVariants[p.variant].threads, kSortVariants[p.variant].items, (unsigned long long)p.ntiles);
     // Two-byte keys alone, from kShortRunsMinN keys: 65 536-bin histogram (counters in the key scratch,
     // which this path does not otherwise need), scan, runs written out.
     if (k.bytes == 2 && val_bytes == 0 && n >= kShortRunsMinN && test_mute_tile(cfg) == 0) {
