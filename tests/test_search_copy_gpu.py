@@ -51,6 +51,30 @@ def test_argmax_types_sizes(kf, dtype, n):
     assert kf.argmax(off) == int(np.argmax(x))
 
 
+def test_argmax_ties_and_nans_at_scale(kf):
+    """Ties across vectors, threads and CTAs go to the smallest index (the kernel keeps a value and the
+    vector that held it per thread and resolves the element afterwards); a NaN never wins against a
+    number, wherever it sits, and an all-NaN array answers its first index."""
+    n = 5_000_017
+    rng = np.random.default_rng(21)
+    for dtype in (np.float32, np.int8, np.uint16, np.float64):
+        x = rng.integers(0, 50, n).astype(dtype)  # thousands of ties for the maximum and the minimum
+        for off in (0, 1, 3):
+            assert kf.argmax(to_dev(x)[off:]) == int(np.argmax(x[off:]))
+            assert kf.argmin(to_dev(x)[off:]) == int(np.argmin(x[off:]))
+        if dtype != np.int8:  # (squares of Int8 values wrap around in the element type)
+            assert kf.argmax1d(kf.abs2, ">", to_dev(x)) == int(np.argmax(x.astype(np.float64) ** 2))
+    y = rng.random(n).astype(np.float32)
+    y[::97] = np.nan
+    y[0] = np.nan
+    want_max = int(np.nanargmax(y))
+    want_min = int(np.nanargmin(y))
+    assert kf.argmax(to_dev(y)) == want_max and kf.argmin(to_dev(y)) == want_min
+    y[want_max + 1:want_max + 5] = y[want_max]  # later ties, with NaNs in between
+    assert kf.argmax(to_dev(y)) == want_max
+    assert kf.argmax(to_dev(np.full(100_000, np.nan, dtype=np.float32))) == 0
+
+
 def test_argmax_extreme_positions(kf):
     n = 3_000_001
     x = np.zeros(n, dtype=np.float32)
