@@ -326,8 +326,48 @@ def primitives_table(kf, torch, peak, iters=10):
     f16 = lambda: kf.sort_(w16, k16, tmp=tmp16)
     for _ in range(2):
         f16()
-    add("sort_i16_keys_2p28", (2 * 2 + 1) * 2 * n, time_gpu(f16, iters, torch), 4)
+    add("sort_i16_keys_2p28", (2 * 2 + 1) * 2 * n, time_gpu(f16, iters, torch), 3)
+    out["sort_i16_keys_2p28"]["note"] = ("keys without payload: 65536-bin histogram, scan and fill (no key moves); bytes counted "
+                                         "as for two 8-bit passes, the DRAM traffic is 4n")
     del k16, w16, tmp16
+    k8 = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=g)
+    w8 = torch.empty_like(k8)
+    tmp8 = kf.get_allocation(kf.Sort1D, k8)
+    f8 = lambda: kf.sort_(w8, k8, tmp=tmp8)
+    for _ in range(2):
+        f8()
+    add("sort_u8_keys_2p28", 3 * n, time_gpu(f8, iters * 2, torch), 3)
+    out["sort_u8_keys_2p28"]["note"] = "keys without payload: histogram, scan and fill; bytes counted as for one 8-bit pass, the DRAM traffic is 2n"
+    tmps8 = kf.get_allocation(kf.Scan1D, kf.identity, "+", k8)
+    fs8 = lambda: kf.scan_("+", w8, k8, tmp=tmps8)
+    for _ in range(3):
+        fs8()
+    add("scan_u8_sum_2p28", 2 * n, time_gpu(fs8, iters * 2, torch), 1)
+    del k8, w8, tmp8, tmps8
+    # the callers one step out: argmax, findfirst (no element matches: the whole array is read), vcopy!
+    from kernelforge_jl_b200.search import gt
+    ws_am = torch.empty(kf.lib.kf_argmax_workspace_bytes(C.F32, n), dtype=torch.uint8, device="cuda")
+    fam = lambda: kf.argmax1d(kf.identity, ">", xf, to_cpu=False, tmp=ws_am)
+    for _ in range(3):
+        fam()
+    add("argmax_f32_2p28", 4 * n, time_gpu(fam, iters * 2, torch), 1)
+    import ctypes
+    import numpy as np
+    two = np.array([2.0], dtype=np.float32)
+    found = torch.empty(1, dtype=torch.int64, device="cuda")
+
+    def ffind():
+        if kf.lib.kf_find(gt(0).code, 0, C.F32, xf.data_ptr(), n, two.ctypes.data_as(ctypes.c_void_p), found.data_ptr(), st) != 0:
+            raise SystemExit("bench: kf_find failed")
+    for _ in range(3):
+        ffind()
+    add("findfirst_f32_2p28_no_match", 4 * n, time_gpu(ffind, iters * 2, torch), 1)
+    cp = torch.empty_like(xf)
+    fcp = lambda: kf.vcopy_(cp, xf)
+    for _ in range(3):
+        fcp()
+    add("vcopy_f32_2p28", 8 * n, time_gpu(fcp, iters * 2, torch), 1)
+    del cp, ws_am
     idx = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
     vout = torch.empty_like(idx)
     tmpp = kf.get_allocation(kf.Sort1D, idx, keys=keys)
