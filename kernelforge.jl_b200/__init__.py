@@ -13,6 +13,7 @@ from .allocations import KernelBuffer, MapReduce1D, Scan1D, Sort1D, get_allocati
 from .mapreduce import mapreduce, mapreduce_, mapreduce1d, mapreduce1d_
 from .ops import AffineCompose, QuaternionMul, abs2, identity, prod, sqdiff, sqrt, wsq
 from .scan import scan, scan_
+from .graphs import CapturedStep
 from .search import (argmax, argmax1d, argmin, eq, findfirst, findlast, ge, gt, le, lt, ne, setvalue_, vcopy_)
 from .sort import sort, sort_, sortperm
 
@@ -22,5 +23,5 @@ __all__ = [
     "ArgumentError", "KernelForgeError", "KernelBuffer", "MapReduce1D", "Scan1D", "Sort1D", "get_allocation",
     "mapreduce", "mapreduce_", "mapreduce1d", "mapreduce1d_", "scan", "scan_", "sort", "sort_", "sortperm",
     "AffineCompose", "QuaternionMul", "abs2", "identity", "sqrt", "prod", "sqdiff", "wsq", "lib", "argmax", "argmax1d", "argmin", "findfirst", "findlast", "gt", "lt", "ge", "le",
-    "eq", "ne", "vcopy_", "setvalue_",
+    "eq", "ne", "vcopy_", "setvalue_", "CapturedStep",
 ]
