@@ -429,6 +429,26 @@ def run_case(args):
         else:
             tmp = kf.get_allocation(kf.Sort1D, keys)
             fn, nbytes = (lambda: kf.sort_(out, keys, tmp=tmp)), {"sort_u64": 136, "sort_u8": 3, "sort_i16": 10}.get(case, 36) * n
+    elif case in ("argmax_f32", "findfirst_f32", "vcopy_f32"):
+        x = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
+        tmp = kf.get_allocation(kf.MapReduce1D, kf.identity, "+", x)  # (only so that the common status check below has a workspace)
+        kf.mapreduce_(kf.identity, "+", torch.empty(1, dtype=torch.float32, device="cuda"), x, tmp=tmp)
+        if case == "argmax_f32":
+            from kernelforge_jl_b200 import _cabi as C
+            ws = torch.empty(kf.lib.kf_argmax_workspace_bytes(C.F32, n), dtype=torch.uint8, device="cuda")
+            fn, nbytes = (lambda: kf.argmax1d(kf.identity, ">", x, to_cpu=False, tmp=ws)), 4 * n
+        elif case == "findfirst_f32":  # no element matches: the whole array is read
+            import ctypes
+            import numpy as np
+            from kernelforge_jl_b200 import _cabi as C
+            two = np.array([2.0], dtype=np.float32)
+            found = torch.empty(1, dtype=torch.int64, device="cuda")
+            st = torch.cuda.current_stream().cuda_stream
+            fn = lambda: kf.lib.kf_find(C.PRED_GT, 0, C.F32, x.data_ptr(), n, two.ctypes.data_as(ctypes.c_void_p), found.data_ptr(), st)
+            nbytes = 4 * n
+        else:
+            y = torch.empty_like(x)
+            fn, nbytes = (lambda: kf.vcopy_(y, x)), 8 * n
     else:
         raise SystemExit("unknown --case %r" % case)
     fn()
@@ -917,7 +937,7 @@ def main():
     ap.add_argument("--detail", type=int, default=1, help="1: also measure the other primitives (single GPU)")
     ap.add_argument("--case", default=None,
                     help="run ONE primitive a few times at n=2^log2n and exit (small case for profiler captures): "
-                         "scan_u32, scan_f32, scan_f64, scan_u8, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_u64, sort_u8, sort_i16, sort_pairs")
+                         "scan_u32, scan_f32, scan_f64, scan_u8, scan_affine, mapreduce_f32, sort_u32, sort_f32, sort_u64, sort_u8, sort_i16, sort_pairs, argmax_f32, findfirst_f32, vcopy_f32")
     ap.add_argument("--log2n", type=int, default=26)
     ap.add_argument("--n", type=int, default=0, help="with --case: an exact element count instead of 2^log2n")
     ap.add_argument("--sharded", action="store_true",
