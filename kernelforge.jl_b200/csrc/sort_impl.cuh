@@ -71,14 +71,12 @@ sort_histogram_kernel(const KeyT *__restrict__ keys, u64 n, u64 *ghist, int sign
     for (u32 i = tid; i < P * kRadix; i += THREADS) sh[i] = 0;
     __syncthreads();
 
+    // Raw bytes are counted; the sign flip of the top digit (signed and float keys) is a permutation of
+    // that digit's bins and is applied once, when the bins are added to the global histogram.
     auto count_key = [&](KeyT k) {
         const KeyT b = radix_bits<KeyT, IS_FLOAT>(k);
 #pragma unroll
-        for (int p = 0; p < P; ++p) {
-            u32 d = (u32)(b >> (8 * p)) & 0xFFu;
-            if (p == P - 1 && signed_or_float) d ^= 0x80u;
-            atomicAdd(&sh[p * kRadix + d], 1u);
-        }
+        for (int p = 0; p < P; ++p) atomicAdd(&sh[p * kRadix + ((u32)(b >> (8 * p)) & 0xFFu)], 1u);
     };
 
     const u64 mis = ((uintptr_t)keys & 15u) / sizeof(KeyT);
@@ -116,9 +114,10 @@ sort_histogram_kernel(const KeyT *__restrict__ keys, u64 n, u64 *ghist, int sign
         if (t < n) count_key(keys[t]);
     }
     __syncthreads();
+    const u32 top_flip = signed_or_float ? 0x80u : 0u;
     for (u32 i = tid; i < P * kRadix; i += THREADS) {
         const u32 c = sh[i];
-        if (c) atomicAdd(&ghist[i], (u64)c);
+        if (c) atomicAdd(&ghist[i ^ (i >= (u32)(P - 1) * kRadix ? top_flip : 0u)], (u64)c);
     }
 }
 
@@ -138,14 +137,12 @@ sort_histogram_lanes_kernel(const KeyT *__restrict__ keys, u64 n, u64 *ghist, in
     for (u32 i = tid; i < P * kRadix * 32; i += THREADS) sh[i] = 0;
     __syncthreads();
 
+    // Raw bytes are counted (the sign flip of the top digit is applied to the bin index at the end).
+    u32 *my = sh + lane;
     auto count_key = [&](KeyT k) {
         const KeyT b = is_float ? radix_bits<KeyT, sizeof(KeyT) >= 4>(k) : k;
 #pragma unroll
-        for (int p = 0; p < P; ++p) {
-            u32 d = (u32)(b >> (8 * p)) & 0xFFu;
-            if (p == P - 1 && signed_or_float) d ^= 0x80u;
-            atomicAdd(&sh[(p * kRadix + d) * 32 + lane], 1u);
-        }
+        for (int p = 0; p < P; ++p) atomicAdd(&my[(p * kRadix + ((u32)(b >> (8 * p)) & 0xFFu)) * 32], 1u);
     };
 
     const u64 mis = ((uintptr_t)keys & 15u) / sizeof(KeyT);
@@ -185,11 +182,12 @@ sort_histogram_lanes_kernel(const KeyT *__restrict__ keys, u64 n, u64 *ghist, in
     __syncthreads();
     // bin i = sum of its 32 lane copies, read in a rotated order so that the 32 threads of a warp
     // (32 consecutive bins, 32 words apart) touch 32 different banks
+    const u32 top_flip = signed_or_float ? 0x80u : 0u;
     for (u32 i = tid; i < P * kRadix; i += THREADS) {
         u32 c = 0;
 #pragma unroll 8
         for (u32 j = 0; j < 32; ++j) c += sh[i * 32 + ((j + lane) & 31u)];
-        if (c) atomicAdd(&ghist[i], (u64)c);
+        if (c) atomicAdd(&ghist[i ^ (i >= (u32)(P - 1) * kRadix ? top_flip : 0u)], (u64)c);
     }
 }
 
