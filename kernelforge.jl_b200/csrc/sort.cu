@@ -89,9 +89,11 @@ __global__ void __launch_bounds__(1024) short_histogram_kernel(const uint16_t *_
     const u64 pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     for (u32 i = tid; i < kShortBins / 2 / 4; i += 1024) reinterpret_cast<uint4 *>(sh_half)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
+    // raw keys are counted; `flip` (0x8000 for signed keys) only swaps which CTA of the pair owns which
+    // half of the raw value range, and is applied to the bin index when the counters are flushed
+    const u32 raw_role = role ^ (flip >> 15);
     auto count_key = [&](u32 k) {
-        const u32 m = k ^ flip;
-        if ((m >> 15) == role) atomicAdd(&sh_half[m & 0x7FFFu], 1u);
+        if ((k >> 15) == raw_role) atomicAdd(&sh_half[k & 0x7FFFu], 1u);
     };
     const u64 mis = ((uintptr_t)keys & 15u) / 2;
     u64 head = mis ? 8 - mis : 0;
@@ -313,6 +315,8 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
         KF_CUDA_TRY(cudaFuncSetAttribute(short_histogram_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
         short_histogram_kernel<<<2 * pairs, 1024, kSmem, s>>>((const uint16_t *)keys_src, n, gcount, flip); note_launch();
         short_scan_kernel<<<1, 1024, 0, s>>>(gcount); note_launch();
+        // a persistent grid here: every CTA starts with a binary search in the 65 537 run starts, which
+        // sit in global memory (one strip per CTA, as for one-byte keys, was measured: 1.70 against 1.63 ms at 2^30)
         const u64 nvec = n / 8;
         u64 blocks = (nvec + 255) / 256;
         const u64 cap = (u64)device_sm_count() * 8;
@@ -332,11 +336,11 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
     sort_scan_histogram_kernel<<<k.bytes, kRadix, 0, s>>>(ghist); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     if (byte_runs) {
-        const u64 nvec = n / 16;
-        u64 blocks = (nvec + 255) / 256;
-        const u64 cap = (u64)device_sm_count() * 8;
-        if (blocks > cap) blocks = cap;
+        // four 16-byte stores per thread and as many CTAs as that takes (streaming writes run faster from
+        // many short CTAs than from a persistent grid)
+        u64 blocks = (n / 16 + 1023) / 1024;
         if (blocks < 1) blocks = 1;
+        if (blocks >= (1ull << 31)) return KF_ERR_INVALID_ARG;
         byte_runs_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>((uint8_t *)keys_dst, n, ghist, k.signed_or_float ? 0x80u : 0u); note_launch();
         KF_CUDA_TRY(cudaGetLastError());
         return KF_OK;
