@@ -4,6 +4,7 @@ path), exactly like a non-device array would be in the reference."""
 import math
 import operator
 
+import numpy as np
 import pytest
 import torch
 
@@ -115,3 +116,35 @@ def test_committed_launch_table_matches_the_header_and_the_sweep():
             assert (m.group(1), int(m.group(2)), int(l)) in cells
             cited += 1
     assert cited >= 100
+
+
+def test_packed_byte_prefix_arithmetic_of_the_scan_kernel():
+    """The one-byte `+` scan keeps four elements per register. This restates `byte_prefix16` of
+    csrc/scan_impl.cuh with Python integers (PRMT selectors included) and checks it against a plain
+    wrap-around cumulative sum: even and odd bytes travel as two 16-bit lanes per word, so no carry crosses
+    a lane, for every carried-in byte and for saturated inputs."""
+    mask = 0xFFFFFFFF
+
+    def byte_perm(a, b, sel):  # PRMT: result byte i = byte (sel nibble i) of the 8 bytes {a, b}
+        src = [(a >> (8 * i)) & 255 for i in range(4)] + [(b >> (8 * i)) & 255 for i in range(4)]
+        return sum(src[(sel >> (4 * i)) & 7] << (8 * i) for i in range(4))
+
+    def byte_prefix16(words, carry_in):
+        carry = carry_in | (carry_in << 16)
+        out = []
+        for w in words:
+            lo, hi = byte_perm(w, 0, 0x4240), byte_perm(w, 0, 0x4341)
+            s_lo = (lo * 0x00010001 + carry) & mask
+            even, odd = ((hi << 16) + s_lo) & mask, (hi * 0x00010001 + s_lo) & mask
+            out.append(byte_perm(even, odd, 0x6240))
+            carry = byte_perm(odd, 0, 0x4242)
+        return out
+
+    rng = np.random.default_rng(5)
+    cases = [np.full(16, 255, np.uint8), np.zeros(16, np.uint8), np.arange(16, dtype=np.uint8) * 17]
+    cases += [rng.integers(0, 256, 16).astype(np.uint8) for _ in range(500)]
+    for x in cases:
+        for b in (0, 1, 128, 255, int(rng.integers(0, 256))):
+            got = np.array(byte_prefix16([int(v) for v in x.view(np.uint32)], b), dtype=np.uint32).view(np.uint8)
+            want = (np.cumsum(x.astype(np.int64)) + b).astype(np.uint8)
+            assert (got == want).all()
