@@ -41,6 +41,13 @@ inline u32 test_mute_tile(const kf_launch_cfg *cfg) { return cfg ? ((u32)cfg->re
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Programmatic dependent launch (sm_90+): a kernel launched with the programmatic-serialization
+// attribute may be scheduled while its predecessor in the stream is still draining. grid_dep_wait()
+// returns once the predecessor has completed and its writes are visible; grid_dep_launch() tells the
+// scheduler that, as far as this CTA is concerned, the successor's CTAs may be brought onto the SMs.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------
 // Raw memory access
 // ---------------------------------------------------------------------------------------------

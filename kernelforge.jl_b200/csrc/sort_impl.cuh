@@ -281,6 +281,9 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
     const KeyT *kin = static_cast<const KeyT *>(a.keys_in);
     KeyT *kout = static_cast<KeyT *>(a.keys_out);
 
+    // The passes are launched with programmatic serialization: this grid may be resident before the
+    // pass (or the bin scan) before it has finished, so nothing it wrote is touched before this point.
+    grid_dep_wait();
     if (tid == 0) {
         const u32 t = atomicAdd(&a.header[kTicketBase + 1 + a.pass], 1u);
         s_misc[8] = t;
@@ -323,6 +326,7 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 256 ? 3 : (THREADS <= 512
         }
     }
 
+    grid_dep_launch();  // the next pass's CTAs may take the SM slots that this grid's last wave frees
     // ---- 2. rank each key within (unit, digit), in element order ---------------------------------
     // Word of the unit's table: {mask of the unit's lanes holding this digit in the current item : 16 |
     // keys of this digit in the unit's earlier items : 16}. Per item: (A) add my lane bit; warp barrier;
@@ -520,8 +524,18 @@ int onesweep_launch_one(const SortPassArgs &a, cudaStream_t s) {
     auto kern = onesweep_kernel<KeyT, IS_FLOAT, ValT, THREADS, ITEMS>;
     if (SM::kBytes > 227 * 1024) return KF_ERR_UNSUPPORTED;
     KF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes));
-    kern<<<(unsigned)a.ntiles, THREADS, SM::kBytes, s>>>(a); note_launch();
-    KF_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)a.ntiles);
+    lc.blockDim = dim3(THREADS);
+    lc.dynamicSmemBytes = SM::kBytes;
+    lc.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    KF_CUDA_TRY(cudaLaunchKernelEx(&lc, kern, a));
+    note_launch();
     return KF_OK;
 }
 
