@@ -47,6 +47,22 @@ __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a -
 // scheduler that, as far as this CTA is concerned, the successor's CTAs may be brought onto the SMs.
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Host side of the same: launches `kern` so that it may become resident while the kernel before it in
+// the stream drains. The kernel must call grid_dep_wait() before it touches anything that kernel wrote.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s, Args &&...args) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(block);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    return cudaLaunchKernelEx(&lc, kern, static_cast<KArgs>(args)...);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Raw memory access

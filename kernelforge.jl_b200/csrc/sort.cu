@@ -6,6 +6,7 @@ namespace kf {
 
 __global__ void sort_scan_histogram_kernel(u64 *ghist) {
     __shared__ u64 s_warp[kRadix / 32];
+    grid_dep_wait();  // chained behind the histogram kernel
     u64 *h = ghist + (size_t)blockIdx.x * kRadix;
     const u32 tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const u64 c = h[tid];
@@ -30,6 +31,7 @@ __global__ void sort_scan_histogram_kernel(u64 *ghist) {
 __global__ void __launch_bounds__(256) byte_runs_fill_kernel(uint8_t *dst, u64 n, const u64 *gexcl, u32 top_xor) {
     __shared__ u64 s_excl[kRadix + 1];
     const u32 tid = threadIdx.x;
+    grid_dep_wait();  // chained behind the bin scan
     s_excl[tid] = gexcl[tid];
     if (tid == 0) s_excl[kRadix] = n;
     __syncthreads();
@@ -141,6 +143,7 @@ __global__ void __launch_bounds__(1024) short_histogram_kernel(const uint16_t *_
 __global__ void __launch_bounds__(1024) short_scan_kernel(u64 *gcount) {
     __shared__ u64 s_warp[32];
     const u32 tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    grid_dep_wait();  // chained behind the histogram kernel
     u64 *seg = gcount + (size_t)warp * (kShortBins / 32);
     u64 part = 0;
     for (int it = 0; it < kShortBins / 1024; ++it) part += seg[it * 32 + lane];
@@ -169,6 +172,7 @@ __global__ void __launch_bounds__(1024) short_scan_kernel(u64 *gcount) {
 // position (sparse keys: long stretches of empty bins) it falls back to a binary search.
 __global__ void __launch_bounds__(256) short_runs_fill_kernel(uint16_t *dst, u64 n, const u64 *__restrict__ excl, u32 flip) {
     const u32 tid = threadIdx.x;
+    grid_dep_wait();  // chained behind the bin scan
     auto digit_at = [&](u64 j) {  // the largest d with excl[d] <= j, for j < n
         int lo = 0, hi = kShortBins;
         while (hi - lo > 1) {
@@ -314,14 +318,14 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
         constexpr size_t kSmem = (size_t)kShortBins / 2 * 4;
         KF_CUDA_TRY(cudaFuncSetAttribute(short_histogram_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
         short_histogram_kernel<<<2 * pairs, 1024, kSmem, s>>>((const uint16_t *)keys_src, n, gcount, flip); note_launch();
-        short_scan_kernel<<<1, 1024, 0, s>>>(gcount); note_launch();
+        KF_CUDA_TRY(launch_chained(short_scan_kernel, 1u, 1024u, 0, s, gcount)); note_launch();
         // a persistent grid here: every CTA starts with a binary search in the 65 537 run starts, which
         // sit in global memory (one strip per CTA, as for one-byte keys, was measured: 1.70 against 1.63 ms at 2^30)
         const u64 nvec = n / 8;
         u64 blocks = (nvec + 255) / 256;
         const u64 cap = (u64)device_sm_count() * 8;
         if (blocks > cap) blocks = cap;
-        short_runs_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>((uint16_t *)keys_dst, n, gcount, flip); note_launch();
+        KF_CUDA_TRY(launch_chained(short_runs_fill_kernel, (unsigned)blocks, 256u, 0, s, (uint16_t *)keys_dst, n, (const u64 *)gcount, flip)); note_launch();
         KF_CUDA_TRY(cudaGetLastError());
         return KF_OK;
     }
@@ -333,7 +337,7 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
     default: rc = sort_hist_k64(k.is_float, keys_src, n, ghist, k.signed_or_float, s); break;
     }
     if (rc != KF_OK) return rc;
-    sort_scan_histogram_kernel<<<k.bytes, kRadix, 0, s>>>(ghist); note_launch();
+    KF_CUDA_TRY(launch_chained(sort_scan_histogram_kernel, (unsigned)k.bytes, (unsigned)kRadix, 0, s, ghist)); note_launch();
     KF_CUDA_TRY(cudaGetLastError());
     if (byte_runs) {
         // four 16-byte stores per thread and as many CTAs as that takes (streaming writes run faster from
@@ -341,7 +345,9 @@ static int sort_run(int key_dtype, const void *keys_src, void *keys_dst, int val
         u64 blocks = (n / 16 + 1023) / 1024;
         if (blocks < 1) blocks = 1;
         if (blocks >= (1ull << 31)) return KF_ERR_INVALID_ARG;
-        byte_runs_fill_kernel<<<(unsigned)blocks, 256, 0, s>>>((uint8_t *)keys_dst, n, ghist, k.signed_or_float ? 0x80u : 0u); note_launch();
+        KF_CUDA_TRY(launch_chained(byte_runs_fill_kernel, (unsigned)blocks, 256u, 0, s, (uint8_t *)keys_dst, n, (const u64 *)ghist,
+                                   k.signed_or_float ? 0x80u : 0u));
+        note_launch();
         KF_CUDA_TRY(cudaGetLastError());
         return KF_OK;
     }

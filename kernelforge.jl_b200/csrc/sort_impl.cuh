@@ -524,17 +524,7 @@ int onesweep_launch_one(const SortPassArgs &a, cudaStream_t s) {
     auto kern = onesweep_kernel<KeyT, IS_FLOAT, ValT, THREADS, ITEMS>;
     if (SM::kBytes > 227 * 1024) return KF_ERR_UNSUPPORTED;
     KF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::kBytes));
-    cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3((unsigned)a.ntiles);
-    lc.blockDim = dim3(THREADS);
-    lc.dynamicSmemBytes = SM::kBytes;
-    lc.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    lc.attrs = attr;
-    lc.numAttrs = 1;
-    KF_CUDA_TRY(cudaLaunchKernelEx(&lc, kern, a));
+    KF_CUDA_TRY(launch_chained(kern, (unsigned)a.ntiles, THREADS, SM::kBytes, s, a));
     note_launch();
     return KF_OK;
 }
