@@ -269,7 +269,7 @@ def primitives_table(kf, torch, peak, iters=10):
     fn = lambda: kf.mapreduce_(kf.identity, "+", dst1, xf, tmp=tmp)
     for _ in range(3):
         fn()
-    add("mapreduce_f32_sum_2p28", 4 * n, time_gpu(fn, iters * 2, torch), 1)
+    add("mapreduce_f32_sum_2p28", 4 * n, time_gpu(fn, iters * 2, torch), 2)
     # BASELINE config 1 (n = 2^20, launch-bound): the bare C-ABI call, as a Julia `ccall` would issue it
     from kernelforge_jl_b200 import _cabi as C
     small, st = xf[: 1 << 20], torch.cuda.current_stream().cuda_stream
@@ -280,9 +280,9 @@ def primitives_table(kf, torch, peak, iters=10):
             raise SystemExit("bench: kf_mapreduce failed")
     for _ in range(20):
         fn()
-    add("mapreduce_f32_abs2_2p20", 4 << 20, time_gpu(fn, 1000, torch), 1)
-    out["mapreduce_f32_abs2_2p20"]["note"] = ("per call of kf_mapreduce through ctypes, 1000 back-to-back calls: one "
-                                              "256-byte memset + one kernel; launch-bound")
+    add("mapreduce_f32_abs2_2p20", 4 << 20, time_gpu(fn, 1000, torch), 2)
+    out["mapreduce_f32_abs2_2p20"]["note"] = ("per call of kf_mapreduce through ctypes, 1000 back-to-back calls: a kernel that clears "
+                                              "the 256-byte header and the reduction chained behind it; launch-bound")
     yf = torch.rand(n, dtype=torch.float32, device="cuda", generator=g)
     fn = lambda: kf.mapreduce_(kf.prod, "+", dst1, (xf, yf), tmp=tmp)
     for _ in range(3):

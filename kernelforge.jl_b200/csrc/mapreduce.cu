@@ -104,6 +104,10 @@ mapreduce_kernel(const T *__restrict__ src, u64 n, T *dst, T *partials, u32 *hea
     for (int u = 1; u < UNROLL; ++u) v = Op::template apply<T>(v, acc[u]);
     v = block_reduce<Op, T, THREADS>(v, smem);
 
+    // The kernel is chained behind the one that clears the workspace header (programmatic dependent
+    // launch): everything above only reads the input, so it may run while that kernel is still in flight;
+    // the header (completion counter, status) is first touched here.
+    grid_dep_wait();
     if (tid == 0) {
         partials[blockIdx.x] = v;
         __threadfence();  // partial visible device-wide before the counter moves
@@ -127,6 +131,9 @@ mapreduce_kernel(const T *__restrict__ src, u64 n, T *dst, T *partials, u32 *hea
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
+
+// Clears the 256-byte workspace header (completion counter, status words).
+__global__ void zero_header_kernel(u32 *header) { header[threadIdx.x] = 0; }
 
 struct MrVariant {
     int threads, unroll;
@@ -178,9 +185,9 @@ static int launch_mr(int variant, int blocks, const void *src, u64 n, void *dst,
     T *out = (T *)dst;
     T *part = (T *)partials;
     switch (variant) {
-    case 0: mapreduce_kernel<T, Op, 256, 4><<<blocks, 256, 0, s>>>(in, n, out, part, header, f, g); note_launch(); break;
-    case 1: mapreduce_kernel<T, Op, 512, 4><<<blocks, 512, 0, s>>>(in, n, out, part, header, f, g); note_launch(); break;
-    case 2: mapreduce_kernel<T, Op, 256, 8><<<blocks, 256, 0, s>>>(in, n, out, part, header, f, g); note_launch(); break;
+    case 0: KF_CUDA_TRY(launch_chained(mapreduce_kernel<T, Op, 256, 4>, (unsigned)blocks, 256u, 0, s, in, n, out, part, header, f, g)); note_launch(); break;
+    case 1: KF_CUDA_TRY(launch_chained(mapreduce_kernel<T, Op, 512, 4>, (unsigned)blocks, 512u, 0, s, in, n, out, part, header, f, g)); note_launch(); break;
+    case 2: KF_CUDA_TRY(launch_chained(mapreduce_kernel<T, Op, 256, 8>, (unsigned)blocks, 256u, 0, s, in, n, out, part, header, f, g)); note_launch(); break;
     default: return KF_ERR_UNSUPPORTED;
     }
     KF_CUDA_TRY(cudaGetLastError());
@@ -240,7 +247,8 @@ extern "C" int32_t kf_mapreduce(int32_t f, int32_t op, int32_t g, int32_t dtype,
     cudaStream_t s = (cudaStream_t)stream;
     u32 *header = (u32 *)ws;
     void *partials = (char *)ws + kHeaderBytes;
-    KF_CUDA_TRY(cudaMemsetAsync(header, 0, kHeaderBytes, s));
+    // a kernel of the library instead of a memset node, so that the reduction can be chained behind it
+    zero_header_kernel<<<1, kHeaderBytes / 4, 0, s>>>(header); note_launch();
     switch (dtype) {
     case KF_U8: return dispatch_mr_op<uint8_t>(op, variant, blocks, src, n, dst, partials, header, f, g, s);
     case KF_I8: return dispatch_mr_op<int8_t>(op, variant, blocks, src, n, dst, partials, header, f, g, s);

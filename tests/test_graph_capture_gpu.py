@@ -26,7 +26,7 @@ def test_captured_step_replays_scan_mapreduce_and_sort(kf, oracle):
         kf.sort_(sorted_keys, keys, tmp=tmp_sort)
 
     captured = kf.CapturedStep(step)
-    assert captured.launches == 1 + 1 + 6  # scan kernel, reduction kernel, histogram + bin scan + 4 passes
+    assert captured.launches == 1 + 2 + 6  # scan kernel; header clear + reduction; histogram + bin scan + 4 passes
     before = int(kf.lib.kf_launch_count())
     for trial in range(3):  # new data in the same buffers, then one replay
         hx = rng.integers(0, 256, n).astype(np.uint32)
