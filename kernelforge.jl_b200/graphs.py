@@ -1,6 +1,6 @@
 """CUDA-graph capture of a sequence of library calls.
 
-Every entry point of libkf_b200.so is a fixed sequence of stream operations (a workspace memset and one
+Every entry point of libkf_b200.so is a fixed sequence of stream operations (the workspace clear and one
 or a few kernel launches, no host synchronisation, no allocation when `tmp=` is given), so a step made
 of several calls can be recorded once and replayed with a single launch. Replaying removes the gaps
 between the memsets and kernels of consecutive calls (about 3 % of a step of two 2^28-element scans).
