@@ -148,3 +148,20 @@ def test_packed_byte_prefix_arithmetic_of_the_scan_kernel():
             got = np.array(byte_prefix16([int(v) for v in x.view(np.uint32)], b), dtype=np.uint32).view(np.uint8)
             want = (np.cumsum(x.astype(np.int64)) + b).astype(np.uint8)
             assert (got == want).all()
+
+
+def test_quaternion_operator_on_the_host(kf):
+    """`QuaternionMul()` is a singleton whose host-side call is the Hamilton product (i*j = k, j*i = -k);
+    like every operator of this layer it has no CPU execution path for arrays, and it is a scan operator
+    only."""
+    q = kf.QuaternionMul()
+    assert q is kf.QuaternionMul() and repr(q) == "QuaternionMul()"
+    one, i, j, k = (1, 0, 0, 0), (0, 1, 0, 0), (0, 0, 1, 0), (0, 0, 0, 1)
+    neg = lambda t: tuple(-v for v in t)
+    assert q(i, j) == k and q(j, i) == neg(k) and q(j, k) == i and q(k, i) == j
+    assert q(i, i) == neg(one) and q(q(i, j), k) == neg(one) and q(one, k) == k
+    assert q((1, 2, 3, 4), (5, 6, 7, 8)) == (-60, 12, 30, 24)
+    with pytest.raises(kf.ArgumentError):
+        kf.scan(q, torch.zeros(8, 4))  # a CPU tensor: there is no CPU path
+    with pytest.raises(kf.ArgumentError):
+        kf.mapreduce(kf.identity, q, torch.zeros(8, 4))
