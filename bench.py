@@ -251,6 +251,37 @@ def time_gpu(fn, iters, torch, sync_each=False):
     return start.elapsed_time(stop) / iters
 
 
+CSV_COLUMNS = ["n", "type", "method", "mean_kernel_us", "std_kernel_us", "mean_total_us", "std_total_us",
+               "bytes_algorithmic", "gbps", "pct_roofline", "gpus"]
+
+
+def primitives_csv_rows(primitives, gpus, peak):
+    """The `primitives` table as rows of the reference's benchmark CSV
+    (`n,type,method,mean_kernel_us,std_kernel_us,mean_total_us,std_total_us`, perfs/julia/bench_utils.jl:7-22 of
+    KernelForge.jl) with `bytes_algorithmic,gbps,pct_roofline,gpus` added. `mean_total_us` is the device time of
+    one library call (its workspace clear included); the kernel-only and spread columns stay empty, this
+    bench does not measure them. `n` and `type` are read from the entry's name (`..._f32_..._2p28...`)."""
+    import re
+    rows = []
+    for name, v in primitives.items():
+        m = re.search(r"_2p(\d+)", name)
+        t = re.search(r"_(f32x2|f32|f64|u8|i8|u16|i16|u32|i32|u64|i64)(?=_|$)", name)
+        gbps = float(v["GB/s"])
+        rows.append({"n": (1 << int(m.group(1))) if m else "", "type": t.group(1) if t else "", "method": "kf_b200:" + name,
+                     "mean_kernel_us": "", "std_kernel_us": "", "mean_total_us": round(float(v["ms"]) * 1e3, 3), "std_total_us": "",
+                     "bytes_algorithmic": v.get("algorithmic_bytes", ""), "gbps": gbps,
+                     "pct_roofline": round(100.0 * gbps / (peak * gpus), 2), "gpus": gpus})
+    return rows
+
+
+def write_primitives_csv(path, primitives, gpus, peak):
+    import csv
+    with open(path, "w", newline="") as fh:
+        w = csv.DictWriter(fh, fieldnames=CSV_COLUMNS)
+        w.writeheader()
+        w.writerows(primitives_csv_rows(primitives, gpus, peak))
+
+
 def primitives_table(kf, torch, peak, iters=10):
     """Effective GB/s of every other configuration of the path at its full size, one GPU."""
     out = {}
@@ -920,6 +951,8 @@ def run_gpu_arm(args):
                         prim[k]["cpu"] = v
         if prim is not None:
             line["primitives"] = prim
+        if args.csv:
+            write_primitives_csv(args.csv, prim, world, peak)
         print(json.dumps(line))
     if world > 1:
         group.close()
@@ -945,6 +978,7 @@ def main():
                          "array of 2^--global-log2n elements split across the ranks; strong scaling)")
     ap.add_argument("--global-log2n", type=int, default=32)
     ap.add_argument("--e2e-chunk-mb", type=int, default=32, help="chunk size of the host-buffer pipeline (MiB)")
+    ap.add_argument("--csv", default=None, help="also write the primitives table to this file in the reference's benchmark CSV schema")
     args = ap.parse_args()
     if args.case:
         return run_case(args)
